@@ -1,0 +1,25 @@
+"""B200-native sliding-window causal 2-simplicial attention (forward + backward).
+
+Drop-in for the sliding path of lucidrains/simplicial-attention:
+``SlidingWindowTwoSimplicialMHA``, ``sliding_two_simplicial_attn`` and
+``SlidingTwoSimplicialAttention`` keep the reference's signatures and run on
+hand-written sm_100a CUDA kernels behind the C ABI of ``include/sa2.h``.
+"""
+from .attention import (
+    SlidingTwoSimplicialAttention,
+    sa2_backward,
+    sa2_forward,
+    sliding_two_simplicial_attn,
+    sliding_two_simplicial_attn_with_lse,
+)
+from .mha import HigherOrderAttention, SlidingWindowTwoSimplicialMHA
+
+__all__ = [
+    "SlidingTwoSimplicialAttention",
+    "sliding_two_simplicial_attn",
+    "sliding_two_simplicial_attn_with_lse",
+    "sa2_forward",
+    "sa2_backward",
+    "HigherOrderAttention",
+    "SlidingWindowTwoSimplicialMHA",
+]

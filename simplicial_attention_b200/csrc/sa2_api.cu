@@ -1,0 +1,183 @@
+// C ABI of the library (declared in include/sa2.h): argument checks, kernel
+// selection and launches.  No torch types, no allocation, no host sync.
+#include "sa2.h"
+#include "sa2_common.cuh"
+#include "sa2_simt.cuh"
+#include "sa2_tc.cuh"
+
+namespace {
+
+using sa2::KernelParams;
+using sa2::TensorRef;
+
+inline TensorRef ref(const void *p, const sa2_strides &s) {
+    return TensorRef{const_cast<void *>(p), s.batch, s.seq, s.head};
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool strides_ok(const sa2_strides &s) { return s.batch % 4 == 0 && s.seq % 4 == 0 && s.head % 4 == 0; }
+
+int check_shape(const sa2_shape &s) {
+    if (s.b <= 0 || s.n <= 0 || s.hq <= 0 || s.hk <= 0 || s.w1 <= 0 || s.w2 <= 0) return SA2_ERR_INVALID;
+    if (s.off1 < 0 || s.off2 < 0) return SA2_ERR_INVALID;
+    if (s.hq % s.hk != 0) return SA2_ERR_INVALID;
+    if (s.d != 32 && s.d != 64 && s.d != 128) return SA2_ERR_UNSUPPORTED;
+    if (s.dtype != SA2_F32 && s.dtype != SA2_BF16) return SA2_ERR_UNSUPPORTED;
+    if (s.kernel != SA2_KERNEL_AUTO && s.kernel != SA2_KERNEL_SIMT && s.kernel != SA2_KERNEL_TCGEN05)
+        return SA2_ERR_UNSUPPORTED;
+    return SA2_OK;
+}
+
+void fill_common(KernelParams &p, const sa2_shape &s) {
+    p.b = s.b; p.n = s.n; p.hq = s.hq; p.hk = s.hk; p.g = s.hq / s.hk;
+    p.w1 = s.w1; p.w2 = s.w2; p.off1 = s.off1; p.off2 = s.off2;
+    p.nk1 = s.n + s.off1; p.nk2 = s.n + s.off2;
+    p.in_bf16 = (s.dtype == SA2_BF16);
+    p.grad_bf16 = 0;
+    p.scale = s.scale;
+}
+
+template <typename K>
+int set_smem(K kernel, size_t bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess
+               ? SA2_OK : SA2_ERR_CUDA;
+}
+
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? SA2_OK : SA2_ERR_CUDA; }
+
+template <int D>
+int simt_fwd(const KernelParams &p, cudaStream_t st) {
+    using namespace sa2::simt;
+    auto k = row_kernel<D, MODE_FWD>;
+    if (int e = set_smem(k, Cfg<D>::smem_fwd)) return e;
+    dim3 grid((p.n + TILE - 1) / TILE, p.hq, p.b);
+    k<<<grid, NTHREADS, Cfg<D>::smem_fwd, st>>>(p);
+    return launch_status();
+}
+
+template <int D>
+int simt_bwd(const KernelParams &p, cudaStream_t st) {
+    using namespace sa2::simt;
+    const int64_t rows = (int64_t)p.b * p.n * p.hq;
+    delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(p, D);
+    if (int e = launch_status()) return e;
+
+    auto kq = row_kernel<D, MODE_BWD_Q>;
+    auto kk2 = row_kernel<D, MODE_BWD_K2>;
+    auto kk1 = k1_kernel<D>;
+    if (int e = set_smem(kq, Cfg<D>::smem_bwd)) return e;
+    if (int e = set_smem(kk2, Cfg<D>::smem_bwd)) return e;
+    if (int e = set_smem(kk1, Cfg<D>::smem_bwd)) return e;
+
+    kq<<<dim3((p.n + TILE - 1) / TILE, p.hq, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
+    if (int e = launch_status()) return e;
+    kk2<<<dim3((p.nk2 + TILE - 1) / TILE, p.hk, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
+    if (int e = launch_status()) return e;
+    kk1<<<dim3((p.nk1 + TILE - 1) / TILE, p.hk, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
+    return launch_status();
+}
+
+}  // namespace
+
+extern "C" {
+
+int sa2_version(void) { return 100; }
+
+const char *sa2_strerror(int status) {
+    switch (status) {
+        case SA2_OK: return "ok";
+        case SA2_ERR_INVALID: return "invalid argument (null pointer, bad size, hq % hk != 0, misaligned pointer or stride)";
+        case SA2_ERR_UNSUPPORTED: return "unsupported configuration (head dim must be 32, 64 or 128; dtype fp32 or bf16; "
+                                         "the tcgen05 kernels need bf16)";
+        case SA2_ERR_WORKSPACE: return "workspace missing, misaligned or smaller than sa2_bwd_workspace_bytes()";
+        case SA2_ERR_CUDA: return "a CUDA call failed";
+        case SA2_ERR_DEVICE: return "a kernel gave up on a bounded wait";
+        default: return "unknown status";
+    }
+}
+
+int sa2_kernel_launches(const sa2_shape *s, int backward) {
+    if (!s || check_shape(*s) != SA2_OK) return -1;
+    const bool tc_ok = backward ? sa2::tc::bwd_supported(*s) : sa2::tc::fwd_supported(*s);
+    if (s->kernel == SA2_KERNEL_TCGEN05 && !tc_ok) return -1;
+    if (tc_ok && s->kernel != SA2_KERNEL_SIMT) return sa2::tc::launches(*s, backward != 0);
+    return backward ? 4 : 1;   // SIMT: delta + dQ + dK2/dV2 + dK1/dV1
+}
+
+size_t sa2_bwd_workspace_bytes(const sa2_shape *s) {
+    if (!s || check_shape(*s) != SA2_OK) return 0;
+    size_t delta = (size_t)s->b * s->hq * s->n * sizeof(float);
+    delta = (delta + 255) & ~(size_t)255;
+    return delta + sa2::tc::bwd_extra_workspace_bytes(*s);
+}
+
+int sa2_fwd(const sa2_fwd_args *a) {
+    if (!a) return SA2_ERR_INVALID;
+    if (int e = check_shape(a->shape)) return e;
+    if (!a->q || !a->k1 || !a->k2 || !a->v1 || !a->v2 || !a->out || !a->lse) return SA2_ERR_INVALID;
+    const void *ptrs[] = {a->q, a->k1, a->k2, a->v1, a->v2, a->out};
+    for (const void *p : ptrs) if (!aligned16(p)) return SA2_ERR_INVALID;
+    const sa2_strides *ss[] = {&a->sq, &a->sk1, &a->sk2, &a->sv1, &a->sv2, &a->sout};
+    for (const sa2_strides *s : ss) if (!strides_ok(*s)) return SA2_ERR_INVALID;
+
+    KernelParams p{};
+    fill_common(p, a->shape);
+    p.q = ref(a->q, a->sq); p.k1 = ref(a->k1, a->sk1); p.k2 = ref(a->k2, a->sk2);
+    p.v1 = ref(a->v1, a->sv1); p.v2 = ref(a->v2, a->sv2); p.out = ref(a->out, a->sout);
+    p.lse = a->lse;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+
+    const bool tc_ok = sa2::tc::fwd_supported(a->shape);
+    if (a->shape.kernel == SA2_KERNEL_TCGEN05 && !tc_ok) return SA2_ERR_UNSUPPORTED;
+    if (tc_ok && a->shape.kernel != SA2_KERNEL_SIMT) return sa2::tc::fwd(p, a->shape, st);
+
+    switch (a->shape.d) {
+        case 32: return simt_fwd<32>(p, st);
+        case 64: return simt_fwd<64>(p, st);
+        default: return simt_fwd<128>(p, st);
+    }
+}
+
+int sa2_bwd(const sa2_bwd_args *a) {
+    if (!a) return SA2_ERR_INVALID;
+    if (int e = check_shape(a->shape)) return e;
+    if (!a->q || !a->k1 || !a->k2 || !a->v1 || !a->v2 || !a->out || !a->dout || !a->lse) return SA2_ERR_INVALID;
+    if (!a->dq || !a->dk1 || !a->dk2 || !a->dv1 || !a->dv2) return SA2_ERR_INVALID;
+    if (a->grad_dtype != SA2_F32 && a->grad_dtype != SA2_BF16) return SA2_ERR_UNSUPPORTED;
+    const void *ptrs[] = {a->q, a->k1, a->k2, a->v1, a->v2, a->out, a->dout, a->dq, a->dk1, a->dk2, a->dv1, a->dv2};
+    for (const void *p : ptrs) if (!aligned16(p)) return SA2_ERR_INVALID;
+    const sa2_strides *ss[] = {&a->sq, &a->sk1, &a->sk2, &a->sv1, &a->sv2, &a->sout, &a->sdout,
+                               &a->sdq, &a->sdk1, &a->sdk2, &a->sdv1, &a->sdv2};
+    for (const sa2_strides *s : ss) if (!strides_ok(*s)) return SA2_ERR_INVALID;
+    const size_t need = sa2_bwd_workspace_bytes(&a->shape);
+    if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
+        return SA2_ERR_WORKSPACE;
+
+    KernelParams p{};
+    fill_common(p, a->shape);
+    p.grad_bf16 = (a->grad_dtype == SA2_BF16);
+    p.q = ref(a->q, a->sq); p.k1 = ref(a->k1, a->sk1); p.k2 = ref(a->k2, a->sk2);
+    p.v1 = ref(a->v1, a->sv1); p.v2 = ref(a->v2, a->sv2);
+    p.out = ref(a->out, a->sout); p.dout = ref(a->dout, a->sdout);
+    p.dq = ref(a->dq, a->sdq); p.dk1 = ref(a->dk1, a->sdk1); p.dk2 = ref(a->dk2, a->sdk2);
+    p.dv1 = ref(a->dv1, a->sdv1); p.dv2 = ref(a->dv2, a->sdv2);
+    p.lse = const_cast<float *>(a->lse);
+    p.delta = reinterpret_cast<float *>(a->workspace);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+
+    const bool tc_ok = sa2::tc::bwd_supported(a->shape);
+    if (a->shape.kernel == SA2_KERNEL_TCGEN05 && !tc_ok) return SA2_ERR_UNSUPPORTED;
+    if (tc_ok && a->shape.kernel != SA2_KERNEL_SIMT) {
+        size_t delta = (size_t)a->shape.b * a->shape.hq * a->shape.n * sizeof(float);
+        delta = (delta + 255) & ~(size_t)255;
+        return sa2::tc::bwd(p, a->shape, reinterpret_cast<char *>(a->workspace) + delta, st);
+    }
+
+    switch (a->shape.d) {
+        case 32: return simt_bwd<32>(p, st);
+        case 64: return simt_bwd<64>(p, st);
+        default: return simt_bwd<128>(p, st);
+    }
+}
+
+}  // extern "C"

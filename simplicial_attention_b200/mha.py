@@ -1,0 +1,117 @@
+"""Multi-head module around the sliding-window 2-simplicial attention operator.
+
+``SlidingWindowTwoSimplicialMHA`` keeps the constructor, forward signature and
+``state_dict`` keys of the reference module
+(simplicial_attention/triton_two_simplicial_attention.py:1062-1081, built on
+``HigherOrderAttention``, simplicial_attention/simplicial_mha.py:28-138), so
+checkpoints of the reference load unchanged:
+``q_norm.weight, k_norms.{0,1}.weight, v_norms.{0,1}.weight, to_qkv.weight,
+combine_heads.weight`` (+ ``prenorm.weight`` / ``postnorm.weight`` when on).
+
+The projections and norms are plain PyTorch; only ``attend`` is ours.
+"""
+from __future__ import annotations
+
+from functools import partial
+from typing import Callable
+
+from torch.nn import Identity, Linear, Module, ModuleList, RMSNorm
+
+from .attention import divisible_by, exists, sliding_two_simplicial_attn
+
+
+def default(v, d):
+    return v if exists(v) else d
+
+
+class HigherOrderAttention(Module):
+    """Projection / head-split / norm shell with a pluggable ``attend``
+    callable ``attend(queries, keys, values[, causal=True]) -> out``
+    (simplicial_mha.py:41,97-103,131)."""
+
+    def __init__(
+        self,
+        dim,
+        causal=False,
+        dim_head=64,
+        dim_head_values=None,
+        heads=8,
+        key_value_heads=None,
+        number_key_value_sets=2,
+        qk_rmsnorm=True,
+        prenorm=False,
+        postnorm=False,
+        attend: Callable | None = None,
+        head_first_dim=True,
+    ):
+        super().__init__()
+        if not exists(attend):
+            raise ValueError("pass attend=..., or use SlidingWindowTwoSimplicialMHA: this package ships only "
+                             "the sliding-window 2-simplicial attend")
+        self.causal = causal
+        self.scale = dim_head ** -0.5
+        self.heads = heads
+        self.key_value_heads = default(key_value_heads, heads)
+        assert divisible_by(heads, self.key_value_heads)
+        self.query_head_groups = heads // self.key_value_heads
+        self.dim_head = dim_head
+        self.dim_head_values = default(dim_head_values, dim_head)
+        self.kv_sets = number_key_value_sets
+        self.head_first_dim = head_first_dim
+
+        self.prenorm = RMSNorm(dim) if prenorm else Identity()
+        self.postnorm = RMSNorm(dim) if postnorm else Identity()
+
+        self.qk_rmsnorm = qk_rmsnorm
+        if qk_rmsnorm:
+            self.q_norm = RMSNorm(dim_head)
+            self.k_norms = ModuleList([RMSNorm(dim_head) for _ in range(self.kv_sets)])
+            self.v_norms = ModuleList([RMSNorm(dim_head) for _ in range(self.kv_sets)])
+
+        self.split_dims = (
+            heads * dim_head,
+            self.kv_sets * self.key_value_heads * dim_head,
+            self.kv_sets * self.key_value_heads * self.dim_head_values,
+        )
+        self.to_qkv = Linear(dim, sum(self.split_dims), bias=False)
+
+        if causal:
+            attend = partial(attend, causal=causal)
+        self.attend = attend
+
+        self.combine_heads = Linear(heads * self.dim_head_values, dim, bias=False)
+
+    def _split(self, t, heads):
+        b, n, _ = t.shape
+        t = t.view(b, n, heads, -1)
+        return t.transpose(1, 2) if self.head_first_dim else t
+
+    def forward(self, tokens):
+        tokens = self.prenorm(tokens)
+        q, k, v = self.to_qkv(tokens).split(self.split_dims, dim=-1)
+
+        queries = self._split(q, self.heads)
+        # each kv head's slice holds its key sets side by side: [k1 | k2]
+        keys = self._split(k, self.key_value_heads).chunk(self.kv_sets, dim=-1)
+        values = self._split(v, self.key_value_heads).chunk(self.kv_sets, dim=-1)
+
+        if self.qk_rmsnorm:
+            queries = self.q_norm(queries)
+            keys = tuple(norm(t) for norm, t in zip(self.k_norms, keys))
+            values = tuple(norm(t) for norm, t in zip(self.v_norms, values))
+
+        out = self.attend(queries, keys, values)
+
+        if self.head_first_dim:
+            out = out.transpose(1, 2)
+        out = out.reshape(out.shape[0], out.shape[1], -1)
+        return self.postnorm(self.combine_heads(out))
+
+
+class SlidingWindowTwoSimplicialMHA(HigherOrderAttention):
+    def __init__(self, *args, w1=512, w2=32, **kwargs):
+        assert "number_key_value_sets" not in kwargs
+        assert "head_first_dim" not in kwargs
+        attend = partial(sliding_two_simplicial_attn, w1=w1, w2=w2, causal=True)
+        super().__init__(*args, number_key_value_sets=2, head_first_dim=False, attend=attend, **kwargs)
+        self.w1, self.w2 = w1, w2

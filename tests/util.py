@@ -1,0 +1,29 @@
+"""Helpers shared by the tests."""
+import glob
+import os
+
+import numpy as np
+import torch
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+NAMES = ("out", "dq", "dk1", "dk2", "dv1", "dv2")
+
+
+def golden_files(prefix=""):
+    return sorted(glob.glob(os.path.join(GOLDEN, prefix + "*.npz")))
+
+
+def load_golden(path):
+    z = np.load(path)
+    t = {k: torch.from_numpy(z[k]) for k in z.files if z[k].ndim > 0}
+    return t, int(z["w1"]), int(z["w2"])
+
+
+def rel_err(x, ref):
+    """max-norm relative error  ||x - ref||_inf / ||ref||_inf"""
+    x, ref = x.detach().double().cpu(), ref.detach().double().cpu()
+    return ((x - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item()
+
+
+def max_abs(x, ref):
+    return (x.detach().double().cpu() - ref.detach().double().cpu()).abs().max().item()
