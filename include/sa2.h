@@ -128,6 +128,16 @@ size_t sa2_bwd_workspace_bytes(const sa2_shape *shape);
  */
 int sa2_kernel_launches(const sa2_shape *shape, int backward);
 
+/*
+ * Device status word of the current device: 0 when every kernel ran to
+ * completion, otherwise the OR of the error bits of kernels that gave up on a
+ * bounded wait (their outputs are then undefined).  Synchronises the device;
+ * meant for tests and diagnostics, not for the hot path.  `reset` != 0 clears
+ * the word.  Returns -1 if the word cannot be read.  No counterpart in the
+ * reference, whose Triton kernels contain no waits.
+ */
+int sa2_device_status(int reset);
+
 /* Static, human-readable text for a status code. */
 const char *sa2_strerror(int status);
 

@@ -7,6 +7,7 @@ hand-written sm_100a CUDA kernels behind the C ABI of ``include/sa2.h``.
 """
 from .attention import (
     SlidingTwoSimplicialAttention,
+    device_status,
     sa2_backward,
     sa2_forward,
     sliding_two_simplicial_attn,
@@ -20,6 +21,7 @@ __all__ = [
     "sliding_two_simplicial_attn_with_lse",
     "sa2_forward",
     "sa2_backward",
+    "device_status",
     "HigherOrderAttention",
     "SlidingWindowTwoSimplicialMHA",
 ]

@@ -17,7 +17,7 @@ KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "tcgen05": KERNEL_TCGEN05}
 
 # symbols declared in include/sa2.h
 EXPORTS = ("sa2_fwd", "sa2_bwd", "sa2_bwd_workspace_bytes", "sa2_strerror", "sa2_version",
-           "sa2_kernel_launches")
+           "sa2_kernel_launches", "sa2_device_status")
 
 
 class Strides(C.Structure):
@@ -86,6 +86,8 @@ def lib() -> C.CDLL:
         handle.sa2_bwd_workspace_bytes.restype = C.c_size_t
         handle.sa2_kernel_launches.argtypes = [C.POINTER(Shape), C.c_int]
         handle.sa2_kernel_launches.restype = C.c_int
+        handle.sa2_device_status.argtypes = [C.c_int]
+        handle.sa2_device_status.restype = C.c_int
         handle.sa2_strerror.argtypes = [C.c_int]
         handle.sa2_strerror.restype = C.c_char_p
         handle.sa2_version.argtypes = []

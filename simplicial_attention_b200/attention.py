@@ -184,3 +184,9 @@ def sliding_two_simplicial_attn_with_lse(q, keys, values, w1=512, w2=32, causal=
     """Same operator, returning ``(out, lse)``; the reference keeps the
     logsumexp private to its autograd function (:740,802)."""
     return sliding_two_simplicial_attn(q, keys, values, w1, w2, causal, kernel=kernel, return_lse=True)
+
+
+def device_status(reset: bool = True) -> int:
+    """Synchronise and return the library's device status word (0 = every kernel
+    ran to completion; non-zero = a kernel gave up on a bounded wait)."""
+    return int(_lib.lib().sa2_device_status(1 if reset else 0))

@@ -83,6 +83,18 @@ extern "C" {
 
 int sa2_version(void) { return 100; }
 
+int sa2_device_status(int reset) {
+    int *word = sa2::tc::status_word();
+    if (!word) return -1;
+    int v = 0;
+    if (cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) return -1;
+    }
+    return v;
+}
+
 const char *sa2_strerror(int status) {
     switch (status) {
         case SA2_OK: return "ok";
@@ -127,7 +139,7 @@ int sa2_fwd(const sa2_fwd_args *a) {
     p.lse = a->lse;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
 
-    const bool tc_ok = sa2::tc::fwd_supported(a->shape);
+    const bool tc_ok = sa2::tc::fwd_supported(a->shape) && sa2::tc::fwd_addressable(p);
     if (a->shape.kernel == SA2_KERNEL_TCGEN05 && !tc_ok) return SA2_ERR_UNSUPPORTED;
     if (tc_ok && a->shape.kernel != SA2_KERNEL_SIMT) return sa2::tc::fwd(p, a->shape, st);
 
