@@ -177,7 +177,7 @@ int sa2_bwd(const sa2_bwd_args *a) {
     p.delta = reinterpret_cast<float *>(a->workspace);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
 
-    const bool tc_ok = sa2::tc::bwd_supported(a->shape);
+    const bool tc_ok = sa2::tc::bwd_supported(a->shape) && sa2::tc::bwd_addressable(p);
     if (a->shape.kernel == SA2_KERNEL_TCGEN05 && !tc_ok) return SA2_ERR_UNSUPPORTED;
     if (tc_ok && a->shape.kernel != SA2_KERNEL_SIMT) {
         size_t delta = (size_t)a->shape.b * a->shape.hq * a->shape.n * sizeof(float);

@@ -3,7 +3,10 @@
 #pragma once
 #include "sa2.h"
 #include "sa2_common.cuh"
+#include "sa2_simt.cuh"
 #include "sa2_tc_fwd.cuh"
+#include "sa2_tc_bwd_k1.cuh"
+#include "sa2_tc_bwd_q.cuh"
 #include "sa2_tmap.cuh"
 
 namespace sa2 {
@@ -16,9 +19,21 @@ inline int tiles_per_query_tile(int w1) { return (w1 + TJ - 1 + TJ - 1) / TJ; } 
 inline bool fwd_supported(const sa2_shape &s) {
     return s.dtype == SA2_BF16 && s.d == 64 && tiles_per_query_tile(s.w1) <= MAX_NT;
 }
-inline bool bwd_supported(const sa2_shape &) { return false; }
-inline size_t bwd_extra_workspace_bytes(const sa2_shape &) { return 0; }
-inline int launches(const sa2_shape &, bool backward) { return backward ? 0 : 1; }
+// The tensor-core backward handles bf16 and head dim 64, any window.
+inline bool bwd_supported(const sa2_shape &s) { return s.dtype == SA2_BF16 && s.d == 64; }
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+inline int bq_splits(int w1) { return (tiles_per_query_tile(w1) + BQ_MAX_TILES - 1) / BQ_MAX_TILES; }
+// dQ/dK2/dV2 run on the tensor cores when their shared accumulators (127 + w2 rows) fit
+inline bool bq_supported(const sa2_shape &s) { return bwd_supported(s) && s.w2 <= BQ_MAX_W2; }
+// scratch after the D vector: per-split partial dQ, then the per-CTA dK2/dV2 slabs
+inline size_t bwd_extra_workspace_bytes(const sa2_shape &s) {
+    if (!bq_supported(s)) return 0;
+    const int ns = bq_splits(s.w1);
+    return align256(bq_part_dq_bytes(s, ns)) + align256(bq_part_k2_bytes(s, ns));
+}
+// forward: 1 kernel; backward: D = rowsum(O*dO), dK1/dV1, dQ/dK2/dV2 partials, their reduction
+// (or, when w2 is too large for the shared accumulators, two fp32 kernels for dQ and dK2/dV2)
+inline int launches(const sa2_shape &, bool backward) { return backward ? 4 : 1; }
 
 inline bool tma_addressable(const TensorRef &t) {
     return (reinterpret_cast<uintptr_t>(t.p) & 15u) == 0 && t.sb % 8 == 0 && t.sn % 8 == 0 && t.sh % 8 == 0;
@@ -66,7 +81,67 @@ inline int fwd(const KernelParams &kp, const sa2_shape &s, cudaStream_t st) {
     return cudaGetLastError() == cudaSuccess ? SA2_OK : SA2_ERR_CUDA;
 }
 
-inline int bwd(const KernelParams &, const sa2_shape &, void *, cudaStream_t) { return SA2_ERR_UNSUPPORTED; }
+inline bool bwd_addressable(const KernelParams &kp) {
+    return fwd_addressable(kp) && tma_addressable(kp.dout);
+}
+
+inline int bwd(const KernelParams &kp, const sa2_shape &s, void *extra, cudaStream_t st) {
+    if (!bwd_addressable(kp)) return SA2_ERR_INVALID;
+    BwdParams P;
+    P.kp = kp;
+    P.c = s.scale * 1.4426950408889634f;
+    P.status = status_word();
+    if (!P.status) return SA2_ERR_CUDA;
+
+    // D_i = sum_c O_ic dO_ic
+    const int64_t rows = (int64_t)kp.b * kp.n * kp.hq;
+    simt::delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(kp, 64);
+    if (cudaGetLastError() != cudaSuccess) return SA2_ERR_CUDA;
+
+    // dK1, dV1: key-tile-owned tcgen05 kernel
+    CUtensorMap mapK, mapV;
+    if (!tmap::make_rows_map(&mapK, kp.k1.p, kp.b, kp.nk1, kp.hk, 64, kp.k1.sb, kp.k1.sn, kp.k1.sh, TJ) ||
+        !tmap::make_rows_map(&mapV, kp.v1.p, kp.b, kp.nk1, kp.hk, 64, kp.v1.sb, kp.v1.sn, kp.v1.sh, TJ))
+        return SA2_ERR_CUDA;
+    if (cudaFuncSetAttribute(bwd_k1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bk1_smem_bytes()) != cudaSuccess)
+        return SA2_ERR_CUDA;
+    bwd_k1_kernel<<<dim3((kp.nk1 + TJ - 1) / TJ, kp.hk, kp.b), BK1_THREADS, bk1_smem_bytes(), st>>>(mapK, mapV, P);
+    if (cudaGetLastError() != cudaSuccess) return SA2_ERR_CUDA;
+
+    if (bq_supported(s)) {
+        // dQ, dK2, dV2: query-tile-owned tcgen05 kernel + deterministic reduction of its partials
+        BqParams Q;
+        Q.kp = kp;
+        Q.c = P.c;
+        Q.nt = tiles_per_query_tile(s.w1);
+        Q.nsplit = bq_splits(s.w1);
+        Q.tiles_per_split = (Q.nt + Q.nsplit - 1) / Q.nsplit;
+        Q.nqt = (kp.n + TQ - 1) / TQ;
+        Q.part_dq = reinterpret_cast<float *>(extra);
+        Q.part_k2 = reinterpret_cast<float *>(reinterpret_cast<char *>(extra) + align256(bq_part_dq_bytes(s, Q.nsplit)));
+        Q.status = P.status;
+        const size_t smem = bq_smem_bytes(s.w2);
+        if (cudaFuncSetAttribute(bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return SA2_ERR_CUDA;
+        bwd_q_kernel<<<dim3(Q.nqt * Q.nsplit, kp.hq, kp.b), BQ_THREADS, smem, st>>>(mapK, mapV, Q);
+        if (cudaGetLastError() != cudaSuccess) return SA2_ERR_CUDA;
+        const int64_t work = ((int64_t)kp.b * kp.n * kp.hq + (int64_t)kp.b * kp.nk2 * kp.hk) * 16;
+        bwd_q_reduce_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(Q);
+        return cudaGetLastError() == cudaSuccess ? SA2_OK : SA2_ERR_CUDA;
+    }
+
+    // dQ and dK2/dV2: fp32 SIMT kernels
+    using namespace sa2::simt;
+    auto kq = row_kernel<64, MODE_BWD_Q>;
+    auto kk2 = row_kernel<64, MODE_BWD_K2>;
+    if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<64>::smem_bwd) != cudaSuccess ||
+        cudaFuncSetAttribute(kk2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<64>::smem_bwd) != cudaSuccess)
+        return SA2_ERR_CUDA;
+    kq<<<dim3((kp.n + TILE - 1) / TILE, kp.hq, kp.b), NTHREADS, Cfg<64>::smem_bwd, st>>>(kp);
+    if (cudaGetLastError() != cudaSuccess) return SA2_ERR_CUDA;
+    kk2<<<dim3((kp.nk2 + TILE - 1) / TILE, kp.hk, kp.b), NTHREADS, Cfg<64>::smem_bwd, st>>>(kp);
+    return cudaGetLastError() == cudaSuccess ? SA2_OK : SA2_ERR_CUDA;
+}
 
 }  // namespace tc
 }  // namespace sa2

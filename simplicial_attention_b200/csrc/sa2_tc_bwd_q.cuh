@@ -1,0 +1,488 @@
+// Backward kernel for dQ, dK2, dV2 on tcgen05 tensor cores (bf16 operands,
+// fp32 accumulation in TMEM, head dim 64), plus the reduction of its partials.
+//
+// A CTA owns 128 query rows i of one (batch, query head) and a subset ("split")
+// of at most three 128-row K1/V1 tiles of their window, resident in shared
+// memory.  Because the backward recomputes probabilities from the saved
+// logsumexp, the splits of one query tile are independent; each writes fp32
+// partials to scratch and a small second kernel adds them in a fixed order
+// (splits, then the query heads of a kv group), so results are reproducible.
+//
+// Per offset e ("sweep") the builder warps form A_e = q_i * k2_{i-e} and
+// B_e = dO_i * v2_{i-e}; per 64-key half-tile the tensor cores compute
+//     S = A_e K1^T      dP = B_e V1^T                 (rows i, columns j)
+// the compute warps (one thread per query row) form
+//     P = exp2(c S - lse2_i)     G = P * (dP - D_i)    (bf16, back into TMEM)
+// and the tensor cores accumulate over the sweep
+//     U_e += G K1       W_e += P V1                    (K1/V1 as MN-major B)
+// At the end of a sweep the row owner folds U_e, W_e into
+//     dQ_i += U_e * k2_{i-e}                           (registers)
+//     dK2_{i-e} += U_e * q_i,  dV2_{i-e} += W_e * dO_i (fp32 rows in shared memory)
+// Row i-e of the shared accumulators is touched by exactly one thread per
+// sweep, so the read-modify-write needs no atomics.
+//
+// Warps (320 threads): 0 TMA producer, 1 MMA issuer + TMEM owner, 2-5 compute,
+// 6-9 builders.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
+// 128h+128); sweep parity p -> U [256+128p, +64), W [320+128p, +64).
+#pragma once
+#include "sa2_tc_bwd_k1.cuh"
+
+namespace sa2 {
+namespace tc {
+
+constexpr int BQ_THREADS = 320;
+constexpr int BQ_MAX_TILES = 3;          // K1/V1 tiles resident per CTA
+constexpr int BQ_ACC_STRIDE = 68;        // floats per accumulator row (64 + 4: conflict-free row-per-thread access)
+constexpr int BQ_MAX_W2 = 56;            // the shared accumulators hold 127 + w2 rows; beyond this they do not fit
+
+enum BqBar {
+    BQ_KV_FULL = 0,
+    BQ_AB_FULL = 1,
+    BQ_AB_EMPTY = 2,
+    BQ_S_FULL = 3,       // [2]
+    BQ_P_FULL = 5,       // [2]
+    BQ_W_FULL = 7,       // [2]
+    BQ_W_EMPTY = 9,      // [2]
+    BQ_BAR_COUNT = 11
+};
+
+enum { ERR_BQ_PRODUCER = 256, ERR_BQ_MMA = 512, ERR_BQ_COMPUTE = 1024, ERR_BQ_BUILDER = 2048 };
+
+struct BqParams {
+    KernelParams kp;
+    float c;            // scale * log2(e)
+    int nt;             // K1/V1 tiles per query tile
+    int nsplit;         // CTAs sharing one query tile
+    int tiles_per_split;
+    int nqt;            // query tiles
+    float *part_dq;     // [nsplit][b][n][hq][64]
+    float *part_k2;     // [b][hq][nqt][nsplit][2][acc_rows][64]   (dK2 slab, then dV2 slab)
+    int *status;
+};
+
+inline int bq_acc_rows(int w2) { return 127 + w2; }
+inline size_t bq_smem_bytes(int w2) {
+    return 1024 + (size_t)2 * BQ_MAX_TILES * TILE_BYTES + 2 * TILE_BYTES +
+           (size_t)2 * bq_acc_rows(w2) * BQ_ACC_STRIDE * sizeof(float) + 256;
+}
+inline size_t bq_part_dq_bytes(const sa2_shape &s, int nsplit) { return (size_t)nsplit * s.b * s.n * s.hq * 64 * sizeof(float); }
+inline size_t bq_part_k2_bytes(const sa2_shape &s, int nsplit) {
+    const size_t nqt = (s.n + TQ - 1) / TQ;
+    return (size_t)s.b * s.hq * nqt * nsplit * 2 * bq_acc_rows(s.w2) * 64 * sizeof(float);
+}
+
+struct BqGeom {
+    int i0, i_last, jbase, t_begin, ntl, nsweeps, upe, total;
+};
+
+__device__ __forceinline__ BqGeom bq_geom(const BqParams &P) {
+    BqGeom g;
+    const KernelParams &kp = P.kp;
+    const int qt = blockIdx.x / P.nsplit, split = blockIdx.x % P.nsplit;
+    g.i0 = qt * TQ;
+    g.i_last = min(g.i0 + TQ - 1, kp.n - 1);
+    g.jbase = g.i0 + kp.off1 + TJ - TJ * P.nt;
+    const int t_first = g.jbase >= 0 ? 0 : min(P.nt - 1, (-g.jbase) / TJ);
+    g.t_begin = max(t_first, split * P.tiles_per_split);
+    const int t_end = min(P.nt, (split + 1) * P.tiles_per_split);
+    g.ntl = max(0, t_end - g.t_begin);
+    g.nsweeps = min(kp.w2, g.i_last + kp.off2 + 1);
+    g.upe = g.ntl * 2;
+    g.total = g.upe * g.nsweeps;
+    return g;
+}
+
+// ---------------------------------------------------------------- builders (warps 6-9)
+__device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, uint8_t *sA, uint8_t *sB,
+                                          uint64_t *bars, volatile int *abort_flag) {
+    const KernelParams &kp = P.kp;
+    const int r = threadIdx.x - 192;
+    const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
+    const int i = g.i0 + r;
+    const bool iv = i < kp.n;
+    const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
+    const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p);
+    uint4 qv[8], dv[8];
+#pragma unroll
+    for (int cc = 0; cc < 8; ++cc) { qv[cc] = make_uint4(0, 0, 0, 0); dv[cc] = make_uint4(0, 0, 0, 0); }
+    if (iv) {
+        const __nv_bfloat16 *qp = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, i, h);
+        const __nv_bfloat16 *dp = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, i, h);
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+            qv[cc] = *reinterpret_cast<const uint4 *>(qp + cc * 8);
+            dv[cc] = *reinterpret_cast<const uint4 *>(dp + cc * 8);
+        }
+    }
+    for (int e = 0; e < g.nsweeps; ++e) {
+        // fetch the second-key rows before waiting, so their latency overlaps the previous sweep
+        const int kk = i + kp.off2 - e;
+        const bool ok = iv && kk >= 0;
+        uint4 kv[8], vv[8];
+        if (ok) {
+            const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, kk, hk);
+            const __nv_bfloat16 *vp2 = v2 + elem_off(kp.v2, b, kk, hk);
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                kv[cc] = *reinterpret_cast<const uint4 *>(kp2 + cc * 8);
+                vv[cc] = *reinterpret_cast<const uint4 *>(vp2 + cc * 8);
+            }
+        }
+        if (e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag)) return ERR_BQ_BUILDER;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+            uint4 a = make_uint4(0, 0, 0, 0), bb = make_uint4(0, 0, 0, 0);
+            if (ok) {
+                a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
+                a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
+                bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
+                bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
+            }
+            *reinterpret_cast<uint4 *>(sA + sw128_offset(r, cc)) = a;
+            *reinterpret_cast<uint4 *>(sB + sw128_offset(r, cc)) = bb;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars[BQ_AB_FULL]);
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------- MMA issuer (warp 1, one lane)
+__device__ __forceinline__ int bq_mma(const BqGeom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sA, uint8_t *sB,
+                                      uint64_t *bars, volatile int *abort_flag) {
+    constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);
+    constexpr uint32_t IDESC_G = idesc_bf16(128, 64, false, true);
+    const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aA = smem_u32(sA), aB = smem_u32(sB);
+
+    auto first = [&](int u) -> bool {
+        const int e = u / g.upe, within = u % g.upe, jt = within >> 1, half = within & 1;
+        if (within == 0 && !mbar_wait(&bars[BQ_AB_FULL], e & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t kt = aK + jt * TILE_BYTES + half * 8192, vt = aV + jt * TILE_BYTES + half * 8192;
+        const uint32_t d = tmem + half * 128;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(d, smem_desc_sw128(aA + 32 * k), smem_desc_sw128(kt + 32 * k), IDESC_F, k > 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(d + 64, smem_desc_sw128(aB + 32 * k), smem_desc_sw128(vt + 32 * k), IDESC_F, k > 0);
+        tc_commit(&bars[BQ_S_FULL + half]);
+        if (within == g.upe - 1) tc_commit(&bars[BQ_AB_EMPTY]);
+        return true;
+    };
+    auto second = [&](int u) -> bool {
+        const int e = u / g.upe, within = u % g.upe, jt = within >> 1, half = within & 1, wb = e & 1;
+        if (!mbar_wait(&bars[BQ_P_FULL + half], (u >> 1) & 1, abort_flag)) return false;
+        if (within == 0 && e >= 2 && !mbar_wait(&bars[BQ_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t kt = aK + jt * TILE_BYTES + half * 8192, vt = aV + jt * TILE_BYTES + half * 8192;
+        const uint32_t a = tmem + half * 128;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            mma_ts(tmem + 256 + wb * 128, a + 64 + 8 * k, smem_desc_sw128(kt + 2048 * k), IDESC_G, (within > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            mma_ts(tmem + 320 + wb * 128, a + 8 * k, smem_desc_sw128(vt + 2048 * k), IDESC_G, (within > 0 || k > 0) ? 1u : 0u);
+        if (within == g.upe - 1) tc_commit(&bars[BQ_W_FULL + wb]);
+        return true;
+    };
+
+    if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_MMA;
+    if (!first(0) || !first(1)) return ERR_BQ_MMA;
+    for (int u = 0; u < g.total; ++u) {
+        if (!second(u)) return ERR_BQ_MMA;
+        if (u + 2 < g.total && !first(u + 2)) return ERR_BQ_MMA;
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------- compute (warps 2-5)
+__device__ __forceinline__ void bq_compute_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ int bq_compute_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
+                                               uint64_t *bars, volatile int *abort_flag) {
+    const KernelParams &kp = P.kp;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ct = threadIdx.x - 64;                  // 0..127 among the compute threads
+    const int r = (warp & 3) * 32 + lane;             // query row within the tile = TMEM lane
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
+    const int split = blockIdx.x % P.nsplit;
+    const int i = g.i0 + r;
+    const bool row_ok = i < kp.n;
+    const float c = P.c;
+    const int acc_rows = 127 + kp.w2;
+
+    // zero the shared accumulators
+    for (int x = ct; x < 2 * acc_rows * BQ_ACC_STRIDE; x += 128) acc_k[x] = 0.f;    // acc_v follows acc_k
+    bq_compute_sync();
+
+    float lse2 = 0.f, dl = 0.f;
+    if (row_ok) {
+        const int64_t o = ((int64_t)b * kp.hq + h) * kp.n + i;
+        lse2 = kp.lse[o] * 1.4426950408889634f;
+        dl = kp.delta[o];
+    }
+    float dq[64];
+#pragma unroll
+    for (int x = 0; x < 64; ++x) dq[x] = 0.f;
+
+    const __nv_bfloat16 *qrow = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, row_ok ? i : 0, h);
+    const __nv_bfloat16 *dorow = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, row_ok ? i : 0, h);
+    const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
+
+    auto drain = [&](int e) -> bool {
+        const int wb = e & 1;
+        if (!warp_wait(&bars[BQ_W_FULL + wb], (e >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const int kk = i + kp.off2 - e;
+        const bool ok = row_ok && kk >= 0;
+        float *ak = acc_k + (size_t)(r + kp.w2 - 1 - e) * BQ_ACC_STRIDE;
+        float *av = acc_v + (size_t)(r + kp.w2 - 1 - e) * BQ_ACC_STRIDE;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            uint32_t u[32], w[32];
+            tmem_ld32(lane_addr + 256 + wb * 128 + hf * 32, u);
+            tmem_ld32(lane_addr + 320 + wb * 128 + hf * 32, w);
+            tmem_wait_ld();
+            if (ok) {
+                const __nv_bfloat16 *kr = k2 + elem_off(kp.k2, b, kk, hk) + hf * 32;
+#pragma unroll
+                for (int v8 = 0; v8 < 4; ++v8) {
+                    const uint4 kraw = *reinterpret_cast<const uint4 *>(kr + v8 * 8);
+                    const uint4 qraw = *reinterpret_cast<const uint4 *>(qrow + hf * 32 + v8 * 8);
+                    const uint4 draw = *reinterpret_cast<const uint4 *>(dorow + hf * 32 + v8 * 8);
+                    const uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
+                    const uint32_t qw[4] = {qraw.x, qraw.y, qraw.z, qraw.w};
+                    const uint32_t dw[4] = {draw.x, draw.y, draw.z, draw.w};
+                    float xk[8], xv[8];
+#pragma unroll
+                    for (int z = 0; z < 4; ++z) {
+                        const __nv_bfloat162 k2v = *reinterpret_cast<const __nv_bfloat162 *>(&kw[z]);
+                        const __nv_bfloat162 q2v = *reinterpret_cast<const __nv_bfloat162 *>(&qw[z]);
+                        const __nv_bfloat162 d2v = *reinterpret_cast<const __nv_bfloat162 *>(&dw[z]);
+                        const int x = v8 * 8 + z * 2;
+                        const float u0 = __uint_as_float(u[x]), u1 = __uint_as_float(u[x + 1]);
+                        const float w0 = __uint_as_float(w[x]), w1 = __uint_as_float(w[x + 1]);
+                        dq[hf * 32 + x] = fmaf(u0, __low2float(k2v), dq[hf * 32 + x]);
+                        dq[hf * 32 + x + 1] = fmaf(u1, __high2float(k2v), dq[hf * 32 + x + 1]);
+                        xk[z * 2] = u0 * __low2float(q2v); xk[z * 2 + 1] = u1 * __high2float(q2v);
+                        xv[z * 2] = w0 * __low2float(d2v); xv[z * 2 + 1] = w1 * __high2float(d2v);
+                    }
+#pragma unroll
+                    for (int f4 = 0; f4 < 2; ++f4) {
+                        float4 *pk = reinterpret_cast<float4 *>(ak + hf * 32 + v8 * 8 + f4 * 4);
+                        float4 *pv = reinterpret_cast<float4 *>(av + hf * 32 + v8 * 8 + f4 * 4);
+                        float4 tk = *pk, tv = *pv;
+                        tk.x += xk[f4 * 4]; tk.y += xk[f4 * 4 + 1]; tk.z += xk[f4 * 4 + 2]; tk.w += xk[f4 * 4 + 3];
+                        tv.x += xv[f4 * 4]; tv.y += xv[f4 * 4 + 1]; tv.z += xv[f4 * 4 + 2]; tv.w += xv[f4 * 4 + 3];
+                        *pk = tk; *pv = tv;
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        mbar_arrive(&bars[BQ_W_EMPTY + wb]);
+        return true;
+    };
+
+    for (int e = 0; e < g.nsweeps; ++e) {
+        const bool sweep_ok = row_ok && (i + kp.off2 - e >= 0);
+        for (int within = 0; within < g.upe; ++within) {
+            const int u = e * g.upe + within, jt = within >> 1, half = within & 1;
+            const int j0 = g.jbase + TJ * (g.t_begin + jt) + 64 * half;
+            const int d1 = i + kp.off1 - j0;
+            const int hi = sweep_ok ? min(d1, 63) : -1;         // valid columns: lo < col <= hi
+            const int lo = max(d1 - kp.w1, -j0 - 1);
+            if (!warp_wait(&bars[BQ_S_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_COMPUTE;
+            tc_fence_after();
+            const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
+            uint32_t pp[32], gg[32];
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t sv[32], dv[32];
+                tmem_ld32(lane_addr + half * 128 + ch * 32, sv);
+                tmem_ld32(lane_addr + half * 128 + 64 + ch * 32, dv);
+                tmem_wait_ld();
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                    float p0 = ex2(fmaf(__uint_as_float(sv[x]), c, -lse2));
+                    float p1 = ex2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
+                    if (!full) {
+                        const int col = ch * 32 + x;
+                        p0 = (col > lo && col <= hi) ? p0 : 0.f;
+                        p1 = (col + 1 > lo && col + 1 <= hi) ? p1 : 0.f;
+                    }
+                    pp[ch * 16 + (x >> 1)] = pack_bf16(p0, p1);
+                    gg[ch * 16 + (x >> 1)] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
+                }
+            }
+            tmem_st32(lane_addr + half * 128, pp);
+            tmem_st32(lane_addr + half * 128 + 64, gg);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars[BQ_P_FULL + half]);
+            if (within == 0 && e >= 1 && !drain(e - 1)) return ERR_BQ_COMPUTE;
+        }
+    }
+    if (g.total > 0 && !drain(g.nsweeps - 1)) return ERR_BQ_COMPUTE;
+
+    // partial dQ of this split
+    if (row_ok) {
+        float *dst = P.part_dq + ((((size_t)split * kp.b + b) * kp.n + i) * kp.hq + h) * 64;
+#pragma unroll
+        for (int x = 0; x < 64; x += 4)
+            *reinterpret_cast<float4 *>(dst + x) = make_float4(dq[x], dq[x + 1], dq[x + 2], dq[x + 3]);
+    }
+    return 0;
+}
+
+__device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
+                                          uint64_t *bars, volatile int *abort_flag) {
+    const KernelParams &kp = P.kp;
+    const int ct = threadIdx.x - 64;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int qt = blockIdx.x / P.nsplit, split = blockIdx.x % P.nsplit;
+    const int acc_rows = 127 + kp.w2;
+    const int err = bq_compute_body(P, g, tmem, acc_k, acc_v, bars, abort_flag);
+    // shared accumulators -> this CTA's slab.  The barrier sits outside the body so that a warp
+    // that gave up on a wait still reaches it.
+    bq_compute_sync();
+    float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + qt) * P.nsplit + split) * (size_t)(2 * acc_rows * 64);
+    for (int x = ct; x < 2 * acc_rows * 16; x += 128) {
+        const int row = x >> 4, c4 = (x & 15) * 4;      // row over both arrays (acc_v follows acc_k)
+        const float4 v = *reinterpret_cast<const float4 *>(acc_k + (size_t)row * BQ_ACC_STRIDE + c4);
+        *reinterpret_cast<float4 *>(slab + (size_t)row * 64 + c4) = v;
+    }
+    return err;
+}
+
+__global__ void __launch_bounds__(BQ_THREADS, 1)
+bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, const BqParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sK = smem;
+    uint8_t *sV = sK + BQ_MAX_TILES * TILE_BYTES;
+    uint8_t *sA = sV + BQ_MAX_TILES * TILE_BYTES;
+    uint8_t *sB = sA + TILE_BYTES;
+    float *acc_k = reinterpret_cast<float *>(sB + TILE_BYTES);
+    const int acc_rows = 127 + P.kp.w2;
+    float *acc_v = acc_k + (size_t)acc_rows * BQ_ACC_STRIDE;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(acc_v + (size_t)acc_rows * BQ_ACC_STRIDE);
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + BQ_BAR_COUNT);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int x = 0; x < BQ_BAR_COUNT; ++x) {
+            const bool many = x == BQ_AB_FULL || (x >= BQ_P_FULL && x < BQ_P_FULL + 2) || (x >= BQ_W_EMPTY && x < BQ_W_EMPTY + 2);
+            mbar_init(&bars[x], many ? 128u : 1u);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_holder;
+    const BqGeom g = bq_geom(P);
+
+    int err = 0;
+    if (warp == 0) {
+        if (lane == 0 && g.total > 0) {
+            const int hk = blockIdx.y / P.kp.g;
+            prefetch_tmap(&mapK);
+            prefetch_tmap(&mapV);
+            mbar_arrive_expect_tx(&bars[BQ_KV_FULL], 2 * TILE_BYTES * g.ntl);
+            for (int t = 0; t < g.ntl; ++t) {
+                const int row = g.jbase + TJ * (g.t_begin + t);
+                tma_load_4d(sK + (size_t)t * TILE_BYTES, &mapK, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+                tma_load_4d(sV + (size_t)t * TILE_BYTES, &mapV, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+            }
+            if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) err = ERR_BQ_PRODUCER;
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && g.total > 0) err = bq_mma(g, tmem, sK, sV, sA, sB, bars, abort_flag);
+        __syncwarp();
+    } else if (warp < 6) {
+        err = bq_compute(P, g, tmem, acc_k, acc_v, bars, abort_flag);
+    } else if (g.total > 0) {
+        err = bq_builder(P, g, sA, sB, bars, abort_flag);
+    }
+    if (err) atomicOr(P.status, err);
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Reduction of the partials: one thread per 4 channels of an output row.
+//   dq[b,i,h]   = scale * sum_split part_dq[split][b][i][h]
+//   dk2[b,k,hk] = scale * sum_{h in group} sum_{tiles touching k} sum_split slab_k[...]
+//   dv2[b,k,hk] =         same over slab_v
+// Row k (position k - off2 in query coordinates) lies in the slab of query tile
+// T at slab row k - off2 - 128 T + (w2 - 1), for the one or two tiles where
+// that index falls inside [0, 127 + w2).
+// ---------------------------------------------------------------------------
+__global__ void bwd_q_reduce_kernel(const BqParams P) {
+    const KernelParams &kp = P.kp;
+    const int acc_rows = 127 + kp.w2;
+    const int64_t nq = (int64_t)kp.b * kp.n * kp.hq * 16;
+    const int64_t nk = (int64_t)kp.b * kp.nk2 * kp.hk * 16;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool gbf16 = kp.grad_bf16 != 0;
+    if (idx < nq) {
+        const int c4 = (int)(idx & 15) * 4;
+        int64_t rest = idx >> 4;
+        const int h = (int)(rest % kp.hq); rest /= kp.hq;
+        const int i = (int)(rest % kp.n);
+        const int b = (int)(rest / kp.n);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < P.nsplit; ++s) {
+            const float4 v = *reinterpret_cast<const float4 *>(P.part_dq + ((((size_t)s * kp.b + b) * kp.n + i) * kp.hq + h) * 64 + c4);
+            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        }
+#pragma unroll
+        for (int z = 0; z < 4; ++z) acc[z] *= kp.scale;
+        store_vec<4>(kp.dq.p, elem_off(kp.dq, b, i, h) + c4, gbf16, acc);
+    } else if (idx < nq + nk) {
+        const int64_t id2 = idx - nq;
+        const int c4 = (int)(id2 & 15) * 4;
+        int64_t rest = id2 >> 4;
+        const int hk = (int)(rest % kp.hk); rest /= kp.hk;
+        const int k = (int)(rest % kp.nk2);
+        const int b = (int)(rest / kp.nk2);
+        float ak[4] = {0.f, 0.f, 0.f, 0.f}, av[4] = {0.f, 0.f, 0.f, 0.f};
+        const int pos = k - kp.off2;                    // in query coordinates (may be negative for halo rows)
+        for (int hh = 0; hh < kp.g; ++hh) {
+            const int h = hk * kp.g + hh;
+            // tiles T with 0 <= pos - 128 T + w2 - 1 < acc_rows
+            const int t_hi = min(P.nqt - 1, (pos + kp.w2 - 1) >= 0 ? (pos + kp.w2 - 1) / TQ : -1);
+            for (int T = max(0, t_hi - 1); T <= t_hi; ++T) {
+                const int row = pos - TQ * T + kp.w2 - 1;
+                if (row < 0 || row >= acc_rows) continue;
+                for (int s = 0; s < P.nsplit; ++s) {
+                    const float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + T) * P.nsplit + s) * (size_t)(2 * acc_rows * 64);
+                    const float4 vk = *reinterpret_cast<const float4 *>(slab + (size_t)row * 64 + c4);
+                    const float4 vv = *reinterpret_cast<const float4 *>(slab + (size_t)(acc_rows + row) * 64 + c4);
+                    ak[0] += vk.x; ak[1] += vk.y; ak[2] += vk.z; ak[3] += vk.w;
+                    av[0] += vv.x; av[1] += vv.y; av[2] += vv.z; av[3] += vv.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int z = 0; z < 4; ++z) ak[z] *= kp.scale;
+        store_vec<4>(kp.dk2.p, elem_off(kp.dk2, b, k, hk) + c4, gbf16, ak);
+        store_vec<4>(kp.dv2.p, elem_off(kp.dv2, b, k, hk) + c4, gbf16, av);
+    }
+}
+
+}  // namespace tc
+}  // namespace sa2

@@ -67,7 +67,11 @@ struct FwdParams {
     int *status;     // device status word
 };
 
-inline size_t fwd_smem_bytes(int nt) { return 1024 + (size_t)nt * 2 * TILE_BYTES + 2 * TILE_BYTES + 256; }
+// at least 120 KB: one CTA per SM, so the 512-column TMEM allocation never waits for a co-resident CTA
+inline size_t fwd_smem_bytes(int nt) {
+    const size_t need = 1024 + (size_t)nt * 2 * TILE_BYTES + 2 * TILE_BYTES + 256;
+    return need > 120 * 1024 ? need : 120 * 1024;
+}
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
