@@ -40,7 +40,8 @@ typedef enum sa2_status {
     SA2_ERR_UNSUPPORTED = 2,   /* head dim not in {32, 64, 128}, unknown dtype, kernel not applicable */
     SA2_ERR_WORKSPACE = 3,     /* workspace missing or smaller than sa2_bwd_workspace_bytes() */
     SA2_ERR_CUDA = 4,          /* a CUDA runtime / driver call failed */
-    SA2_ERR_DEVICE = 5         /* a kernel gave up on a bounded wait */
+    SA2_ERR_DEVICE = 5,        /* a kernel gave up on a bounded wait */
+    SA2_ERR_TOO_LARGE = 6      /* beyond the capacity of sa2_bwd_static_scratch */
 } sa2_status;
 
 typedef enum sa2_dtype { SA2_F32 = 0, SA2_BF16 = 1 } sa2_dtype;
@@ -120,6 +121,34 @@ int sa2_bwd(const sa2_bwd_args *args);
  * itself at :825).  The forward needs none.
  */
 size_t sa2_bwd_workspace_bytes(const sa2_shape *shape);
+
+/*
+ * Backward for callers that cannot supply scratch memory.  It has no
+ * counterpart in the reference, which allocates whatever it needs from torch.
+ *
+ * Who needs it: a host that gave all device memory to its own pools before this
+ * library was loaded, a plug-in that may launch kernels but not call an
+ * allocator, a loop in which allocation is ruled out for latency reasons.
+ * `args->workspace` and `args->workspace_bytes` are ignored; the row sums
+ * D_i = sum_c O_ic dO_ic go into an array compiled into the library
+ * (SA2_STATIC_SCRATCH_ROWS floats = 1 MiB, held by every GPU that loads the
+ * library until the process ends).  The call allocates and frees nothing.
+ *
+ *   - Limit: b * hq * n <= SA2_STATIC_SCRATCH_ROWS, otherwise SA2_ERR_TOO_LARGE.
+ *   - Runs the fp32 kernels (any head dim in {32, 64, 128}, fp32 or bf16
+ *     tensors); shape.kernel == SA2_KERNEL_TCGEN05 is SA2_ERR_UNSUPPORTED
+ *     because the tensor-core backward needs far more scratch than this.
+ *     Results equal sa2_bwd with shape.kernel == SA2_KERNEL_SIMT.
+ *   - The first call on each device looks up the array's device address (the
+ *     device must be current, as for every call); make that first call before
+ *     starting any stream capture.
+ *   - All calls share the one array, which keeps whatever the previous call
+ *     left in it.  Nothing in it has to start at zero - each call rewrites the
+ *     entries it reads - but two calls that overlap in time on the same GPU
+ *     (different streams, or different threads) race on it: keep them ordered.
+ */
+#define SA2_STATIC_SCRATCH_ROWS 262144
+int sa2_bwd_static_scratch(const sa2_bwd_args *args);
 
 /*
  * Number of kernel launches sa2_fwd (backward == 0) or sa2_bwd (backward != 0)

@@ -17,7 +17,8 @@ KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "tcgen05": KERNEL_TCGEN05}
 
 # symbols declared in include/sa2.h
 EXPORTS = ("sa2_fwd", "sa2_bwd", "sa2_bwd_workspace_bytes", "sa2_strerror", "sa2_version",
-           "sa2_kernel_launches", "sa2_device_status")
+           "sa2_kernel_launches", "sa2_device_status", "sa2_bwd_static_scratch")
+STATIC_SCRATCH_ROWS = 262144   # SA2_STATIC_SCRATCH_ROWS in include/sa2.h
 
 
 class Strides(C.Structure):
@@ -82,6 +83,8 @@ def lib() -> C.CDLL:
         handle.sa2_fwd.restype = C.c_int
         handle.sa2_bwd.argtypes = [C.POINTER(BwdArgs)]
         handle.sa2_bwd.restype = C.c_int
+        handle.sa2_bwd_static_scratch.argtypes = [C.POINTER(BwdArgs)]
+        handle.sa2_bwd_static_scratch.restype = C.c_int
         handle.sa2_bwd_workspace_bytes.argtypes = [C.POINTER(Shape)]
         handle.sa2_bwd_workspace_bytes.restype = C.c_size_t
         handle.sa2_kernel_launches.argtypes = [C.POINTER(Shape), C.c_int]

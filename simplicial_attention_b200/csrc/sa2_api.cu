@@ -104,6 +104,8 @@ const char *sa2_strerror(int status) {
         case SA2_ERR_WORKSPACE: return "workspace missing, misaligned or smaller than sa2_bwd_workspace_bytes()";
         case SA2_ERR_CUDA: return "a CUDA call failed";
         case SA2_ERR_DEVICE: return "a kernel gave up on a bounded wait";
+        case SA2_ERR_TOO_LARGE: return "problem too large for the library's built-in scratch: b * hq * n exceeds "
+                                       "SA2_STATIC_SCRATCH_ROWS (use sa2_bwd with a caller-provided workspace)";
         default: return "unknown status";
     }
 }
@@ -185,6 +187,77 @@ int sa2_bwd(const sa2_bwd_args *a) {
         return sa2::tc::bwd(p, a->shape, reinterpret_cast<char *>(a->workspace) + delta, st);
     }
 
+    switch (a->shape.d) {
+        case 32: return simt_bwd<32>(p, st);
+        case 64: return simt_bwd<64>(p, st);
+        default: return simt_bwd<128>(p, st);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Backward without caller-provided scratch.
+//
+// Some hosts of this library cannot hand it a workspace: an inference or
+// training engine that claimed all device memory for its own pools at start-up,
+// a plug-in that is only allowed to launch kernels, a latency-critical loop in
+// which every allocator call is forbidden.  For them the row sums
+// D_i = sum_c O_ic dO_ic live in the fixed device array below instead.  The
+// array is part of the library image: every GPU that loads the library keeps
+// SA2_STATIC_SCRATCH_ROWS * 4 bytes (1 MiB) for it until the process exits.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) float g_static_rowsum[SA2_STATIC_SCRATCH_ROWS];
+
+namespace {
+
+// Device address of g_static_rowsum on the current device.  In host code the
+// array's name is only a handle, never a device pointer, so the address is
+// asked for once per device (with that device current) and remembered.
+float *static_rowsum_ptr() {
+    static float *ptrs[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    float *p = ptrs[dev];
+    if (!p) {
+        void *addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_static_rowsum) != cudaSuccess || !addr) return nullptr;
+        p = reinterpret_cast<float *>(addr);
+        ptrs[dev] = p;      // racing first calls store the same value
+    }
+    return p;
+}
+
+}  // namespace
+
+int sa2_bwd_static_scratch(const sa2_bwd_args *a) {
+    if (!a) return SA2_ERR_INVALID;
+    if (int e = check_shape(a->shape)) return e;
+    if (!a->q || !a->k1 || !a->k2 || !a->v1 || !a->v2 || !a->out || !a->dout || !a->lse) return SA2_ERR_INVALID;
+    if (!a->dq || !a->dk1 || !a->dk2 || !a->dv1 || !a->dv2) return SA2_ERR_INVALID;
+    if (a->grad_dtype != SA2_F32 && a->grad_dtype != SA2_BF16) return SA2_ERR_UNSUPPORTED;
+    const void *ptrs[] = {a->q, a->k1, a->k2, a->v1, a->v2, a->out, a->dout, a->dq, a->dk1, a->dk2, a->dv1, a->dv2};
+    for (const void *p : ptrs) if (!aligned16(p)) return SA2_ERR_INVALID;
+    const sa2_strides *ss[] = {&a->sq, &a->sk1, &a->sk2, &a->sv1, &a->sv2, &a->sout, &a->sdout,
+                               &a->sdq, &a->sdk1, &a->sdk2, &a->sdv1, &a->sdv2};
+    for (const sa2_strides *s : ss) if (!strides_ok(*s)) return SA2_ERR_INVALID;
+    // only the fp32 kernels get by with the row sums alone
+    if (a->shape.kernel == SA2_KERNEL_TCGEN05) return SA2_ERR_UNSUPPORTED;
+    const long long rows = (long long)a->shape.b * a->shape.hq * a->shape.n;
+    if (rows > (long long)SA2_STATIC_SCRATCH_ROWS) return SA2_ERR_TOO_LARGE;
+
+    float *rowsum = static_rowsum_ptr();
+    if (!rowsum) return SA2_ERR_CUDA;
+
+    KernelParams p{};
+    fill_common(p, a->shape);
+    p.grad_bf16 = (a->grad_dtype == SA2_BF16);
+    p.q = ref(a->q, a->sq); p.k1 = ref(a->k1, a->sk1); p.k2 = ref(a->k2, a->sk2);
+    p.v1 = ref(a->v1, a->sv1); p.v2 = ref(a->v2, a->sv2);
+    p.out = ref(a->out, a->sout); p.dout = ref(a->dout, a->sdout);
+    p.dq = ref(a->dq, a->sdq); p.dk1 = ref(a->dk1, a->sdk1); p.dk2 = ref(a->dk2, a->sdk2);
+    p.dv1 = ref(a->dv1, a->sdv1); p.dv2 = ref(a->dv2, a->sdv2);
+    p.lse = const_cast<float *>(a->lse);
+    p.delta = rowsum;     // every entry the kernels read is rewritten first: nothing has to start at zero
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
     switch (a->shape.d) {
         case 32: return simt_bwd<32>(p, st);
         case 64: return simt_bwd<64>(p, st);
