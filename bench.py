@@ -188,6 +188,7 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=("auto", "simt", "tcgen05"))
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
     args = ap.parse_args()
     cfg = dict(WORKLOADS[args.workload])
 
@@ -268,16 +269,18 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- timed, end to end through the autograd API with host buffers
-    for _ in range(2):
-        step_e2e()
-    barrier(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step_e2e()
-    e1.record()
-    barrier(world)
-    e2e_ms = reduce_max(e0.elapsed_time(e1), world)
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        for _ in range(2):
+            step_e2e()
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step_e2e()
+        e1.record()
+        barrier(world)
+        e2e_ms = reduce_max(e0.elapsed_time(e1), world)
 
     if rank != 0:
         if world > 1:
@@ -304,7 +307,7 @@ def main():
         "config": {"workload": args.workload, **cfg, "global_batch": cfg["b"] * world, "kernel": args.kernel,
                    "sharding": "batch x head per rank, no collective", "l2": "256 MB buffer written between timed steps"},
         "tokens_per_s": cfg["b"] * cfg["n"] * world / (ms_per_step * 1e-3),
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+        "e2e": None if args.no_e2e else {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches * args.steps,
         "roofline": {"bound": "tensor", "kernel": "sa2_bwd", "achieved": bwd_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
