@@ -73,11 +73,13 @@ inline int fwd(const KernelParams &kp, const sa2_shape &s, cudaStream_t st) {
     if (!tmap::make_rows_map(&mapK, kp.k1.p, kp.b, kp.nk1, kp.hk, 64, kp.k1.sb, kp.k1.sn, kp.k1.sh, TJ) ||
         !tmap::make_rows_map(&mapV, kp.v1.p, kp.b, kp.nk1, kp.hk, 64, kp.v1.sb, kp.v1.sn, kp.v1.sh, TJ))
         return SA2_ERR_CUDA;
+    CUtensorMap mapK2;      // second keys, 32-row boxes
+    if (!tmap::make_rows_map(&mapK2, kp.k2.p, kp.b, kp.nk2, kp.hk, 64, kp.k2.sb, kp.k2.sn, kp.k2.sh, 32)) return SA2_ERR_CUDA;
     const size_t smem = fwd_smem_bytes(P.nt);
     if (cudaFuncSetAttribute(fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return SA2_ERR_CUDA;
     dim3 grid((kp.n + TQ - 1) / TQ, kp.hq, kp.b);
-    fwd_kernel<<<grid, FWD_THREADS, smem, st>>>(mapK, mapV, P);
+    fwd_kernel<<<grid, FWD_THREADS, smem, st>>>(mapK, mapV, mapK2, P);
     return cudaGetLastError() == cudaSuccess ? SA2_OK : SA2_ERR_CUDA;
 }
 

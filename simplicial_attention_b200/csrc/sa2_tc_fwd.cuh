@@ -6,28 +6,40 @@
 // (bf16, CUDA cores, 128-byte-swizzled shared memory), multiplies it against
 // the TMA-staged K1 tiles of the window (S = A_e K1^T, 128x128x64 per tile,
 // accumulator in TMEM), turns S into P = exp2(c*S - ref) in registers, writes
-// P back to TMEM as bf16 and feeds it as the A operand of W_e += P V1
-// (128x64x128, V1 tile as an MN-major B operand).  At the end of a sweep the
-// row owner adds v2_{i-e} * W_e to its output registers.  The softmax is
-// joint over all (j, e): one reference value, one denominator per row.
+// P to TMEM as bf16 and feeds it as the A operand of W_e += P V1 (128x64x128,
+// V1 tile as an MN-major B operand).  At the end of a sweep the row owner adds
+// v2_{i-e} * W_e to its output registers.  The softmax is joint over all
+// (j, e): one denominator per row.
 //
-// Warp roles (192 threads):
-//   warp 0      TMA producer for the K1/V1 window (loaded once, resident in
-//               shared memory) and builder of the A_e tiles (2 stages)
+// Warp roles (320 threads):
+//   warp 0      TMA producer: the K1/V1 window and the 127 + 32 second-key rows
+//               the tile can pair with, loaded once and resident in shared memory
 //   warp 1      issues every tcgen05.mma (one lane), owns the TMEM allocation
-//   warps 2-5   one thread per query row: softmax, P, output accumulation
+//   warps 2-5   softmax group 0: even sweeps, one thread per query row
+//   warps 6-9   softmax group 1: odd sweeps, one thread per query row
+// A group builds the A tile of its next sweep itself (row r by the thread that
+// owns row r) as soon as the last S product of its current sweep has completed,
+// so the tile is ready long before the tensor cores need it.
+// The MMA warp interleaves the tiles of an even and an odd sweep, so while one
+// group runs the exponentials of its tile the tensor cores work for the other
+// and each SM sub-partition has two softmax warps to hide latencies.  Every
+// group keeps its own (reference, denominator, output) state per row; the two
+// states are merged through shared memory at the end.
 //
-// TMEM columns: S/P buffer 0 [0,128), S/P buffer 1 [128,256), W buffer 0
-// [256,320), W buffer 1 [320,384).  P (bf16, 64 columns) overwrites the first
-// half of the S buffer it was computed from.
+// The unit of the pipeline is half a key tile (64 keys): S = A_e K1[64 rows]^T is
+// 128x64, and every group has two S and two P buffers, so its next unit is
+// ready in TMEM while it works on the current one.
+//
+// TMEM columns, group g, buffer s: S [128g + 64s, +64), P (bf16) [384 + 64g + 32s, +32);
+// W of group g [256 + 64g, +64).
 //
 // Reference handling: probabilities are computed against a per-row reference
-// that is frozen during a sweep, so the W accumulator in TMEM never needs a
-// rescale in the common case; bf16 has fp32's exponent range, so P may exceed 1
-// by many orders of magnitude without loss.  Only when a tile holds a logit
-// more than 2^64 above the reference (always true for the very first tile,
-// whose reference is -inf) does the warp take a slow path: exact tile maximum,
-// rescale of the row's partial sums (including W in TMEM), recomputation of P.
+// that only moves when it must, so the W accumulator in TMEM normally never
+// needs a rescale; bf16 has fp32's exponent range, so P may exceed 1 by many
+// orders of magnitude without loss.  When the probabilities of a tile sum to
+// more than 2^64 (always true for a row's very first tile, whose reference is
+// -inf) the warp takes a slow path: exact tile maximum, rescale of the row's
+// partial sums (including W in TMEM), recomputation of P.
 #pragma once
 #include "sa2_common.cuh"
 #include "sa2_sm100.cuh"
@@ -41,20 +53,21 @@ using namespace sa2::sm100;
 
 constexpr int TQ = 128;          // query rows per CTA
 constexpr int TJ = 128;          // first-key rows per tile
-constexpr int FWD_THREADS = 192;
+constexpr int FWD_THREADS = 320;
 constexpr int MAX_NT = 5;        // K1/V1 tiles resident in shared memory (head dim 64)
 constexpr uint32_t TILE_BYTES = TJ * 64 * 2;
+constexpr int K2_ROWS = 160;     // second-key rows kept in shared memory: positions i0 - 32 ... i0 + 127
 
 enum FwdBar {
-    BAR_KV_FULL = 0,                 // [MAX_NT]
-    BAR_A_FULL = BAR_KV_FULL + MAX_NT,   // [2]
-    BAR_A_EMPTY = BAR_A_FULL + 2,
-    BAR_S_FULL = BAR_A_EMPTY + 2,
-    BAR_P_FULL = BAR_S_FULL + 2,
-    BAR_W_FULL = BAR_P_FULL + 2,
-    BAR_W_EMPTY = BAR_W_FULL + 2,
-    BAR_PV_DONE = BAR_W_EMPTY + 2,
-    BAR_COUNT = BAR_PV_DONE + 2
+    BAR_KV_FULL = 0,                     // [MAX_NT]
+    BAR_A_FULL = BAR_KV_FULL + MAX_NT,   // [2] per group
+    BAR_K2_FULL = BAR_A_FULL + 2,
+    BAR_W_FULL = BAR_K2_FULL + 2,        // [2] per group
+    BAR_W_EMPTY = BAR_W_FULL + 2,        // [2] per group
+    BAR_S_FULL = BAR_W_EMPTY + 2,        // [4] group * 2 + buffer
+    BAR_P_FULL = BAR_S_FULL + 4,         // [4]
+    BAR_PV_DONE = BAR_P_FULL + 4,        // [4]
+    BAR_COUNT = BAR_PV_DONE + 4
 };
 
 // error bits reported through the device status word
@@ -69,7 +82,7 @@ struct FwdParams {
 
 // at least 120 KB: one CTA per SM, so the 512-column TMEM allocation never waits for a co-resident CTA
 inline size_t fwd_smem_bytes(int nt) {
-    const size_t need = 1024 + (size_t)nt * 2 * TILE_BYTES + 2 * TILE_BYTES + 256;
+    const size_t need = 1024 + (size_t)nt * 2 * TILE_BYTES + 2 * TILE_BYTES + K2_ROWS * 128 + 256 + 1024;
     return need > 120 * 1024 ? need : 120 * 1024;
 }
 
@@ -91,14 +104,6 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
     __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
     return *reinterpret_cast<uint32_t *>(&r);
 }
-__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
-    __nv_bfloat162 r = __hmax2(*reinterpret_cast<__nv_bfloat162 *>(&a), *reinterpret_cast<__nv_bfloat162 *>(&b));
-    return *reinterpret_cast<uint32_t *>(&r);
-}
-__device__ __forceinline__ float bf16x2_max_as_float(uint32_t a) {
-    __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&a);
-    return fmaxf(__low2float(v), __high2float(v));
-}
 
 // every lane of the warp waits; the result is uniform so that the .sync.aligned
 // tcgen05 instructions that follow are never reached by a partial warp
@@ -107,7 +112,9 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volati
 }
 
 struct FwdGeom {
-    int i0, i_last, jbase, t_first, ntiles, nsweeps, total;
+    int i0, i_last, jbase, t_first, ntiles, nsweeps;
+    int upe;          // units (half tiles) per sweep
+    int units[2];     // units each group processes: its sweeps x upe
 };
 
 __device__ __forceinline__ FwdGeom fwd_geom(const FwdParams &P) {
@@ -118,120 +125,172 @@ __device__ __forceinline__ FwdGeom fwd_geom(const FwdParams &P) {
     g.t_first = g.jbase >= 0 ? 0 : min(P.nt - 1, (-g.jbase) / TJ);
     g.ntiles = P.nt - g.t_first;
     g.nsweeps = min(P.kp.w2, g.i_last + P.kp.off2 + 1);
-    g.total = g.ntiles * g.nsweeps;
+    g.upe = 2 * g.ntiles;
+    g.units[0] = ((g.nsweeps + 1) / 2) * g.upe;
+    g.units[1] = (g.nsweeps / 2) * g.upe;
     return g;
 }
 
-// ------------------------------------------------------------------ warp 0
-__device__ __forceinline__ int fwd_producer(const FwdParams &P, const FwdGeom &g, const CUtensorMap *mapK, const CUtensorMap *mapV,
-                                            uint8_t *sK, uint8_t *sV, uint8_t *sA, uint64_t *bars, volatile int *abort_flag) {
+// ------------------------------------------------------------------ warp 0 (one lane)
+__device__ __forceinline__ void fwd_producer(const FwdParams &P, const FwdGeom &g, const CUtensorMap *mapK, const CUtensorMap *mapV,
+                                             const CUtensorMap *mapK2, uint8_t *sK, uint8_t *sV, uint8_t *sK2, uint64_t *bars) {
     const KernelParams &kp = P.kp;
-    const int lane = threadIdx.x & 31;
     const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
-    if (lane == 0) {
-        prefetch_tmap(mapK);
-        prefetch_tmap(mapV);
-        for (int t = P.nt - 1; t >= g.t_first; --t) {      // the diagonal tile first
-            mbar_arrive_expect_tx(&bars[BAR_KV_FULL + t], 2 * TILE_BYTES);
-            tma_load_4d(sK + (size_t)t * TILE_BYTES, mapK, &bars[BAR_KV_FULL + t], 0, hk, g.jbase + TJ * t, b);
-            tma_load_4d(sV + (size_t)t * TILE_BYTES, mapV, &bars[BAR_KV_FULL + t], 0, hk, g.jbase + TJ * t, b);
-        }
+    prefetch_tmap(mapK);
+    prefetch_tmap(mapV);
+    prefetch_tmap(mapK2);
+    if (kp.w2 <= 32) {
+        mbar_arrive_expect_tx(&bars[BAR_K2_FULL], K2_ROWS * 128);
+        for (int bx = 0; bx < K2_ROWS / 32; ++bx)
+            tma_load_4d(sK2 + bx * 4096, mapK2, &bars[BAR_K2_FULL], 0, hk, g.i0 + kp.off2 - 32 + 32 * bx, b);
+    } else {
+        mbar_arrive(&bars[BAR_K2_FULL]);
     }
-    const __nv_bfloat16 *q = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p);
-    const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
-    for (int e = 0; e < g.nsweeps; ++e) {
-        const int stage = e & 1;
-        if (e >= 2 && !warp_wait(&bars[BAR_A_EMPTY + stage], ((e >> 1) - 1) & 1, abort_flag)) return ERR_FWD_PRODUCER;
-        uint8_t *dst = sA + (size_t)stage * TILE_BYTES;
-#pragma unroll 4
-        for (int it = 0; it < 32; ++it) {
-            const int chunk = it * 32 + lane;
-            const int r = chunk >> 3, c = chunk & 7;
-            const int i = g.i0 + r, kk = i + kp.off2 - e;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (i < kp.n && kk >= 0) {
-                const uint4 a = *reinterpret_cast<const uint4 *>(q + elem_off(kp.q, b, i, h) + c * 8);
-                const uint4 k = *reinterpret_cast<const uint4 *>(k2 + elem_off(kp.k2, b, kk, hk) + c * 8);
-                v.x = mul_bf16x2(a.x, k.x); v.y = mul_bf16x2(a.y, k.y);
-                v.z = mul_bf16x2(a.z, k.z); v.w = mul_bf16x2(a.w, k.w);
-            }
-            *reinterpret_cast<uint4 *>(dst + sw128_offset(r, c)) = v;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[BAR_A_FULL + stage]);
+    for (int t = P.nt - 1; t >= g.t_first; --t) {      // the diagonal tile first
+        mbar_arrive_expect_tx(&bars[BAR_KV_FULL + t], 2 * TILE_BYTES);
+        tma_load_4d(sK + (size_t)t * TILE_BYTES, mapK, &bars[BAR_KV_FULL + t], 0, hk, g.jbase + TJ * t, b);
+        tma_load_4d(sV + (size_t)t * TILE_BYTES, mapV, &bars[BAR_KV_FULL + t], 0, hk, g.jbase + TJ * t, b);
     }
-    return 0;
 }
 
 // ------------------------------------------------------------------ warp 1 (one lane)
+// Group g's stream: unit r is half tile r % upe of the group's (r / upe)-th sweep, e = 2 (r / upe) + g.
 __device__ __forceinline__ int fwd_mma(const FwdParams &P, const FwdGeom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sA,
                                        uint64_t *bars, volatile int *abort_flag) {
-    constexpr uint32_t IDESC_S = idesc_bf16(128, 128, false, false);
+    constexpr uint32_t IDESC_S = idesc_bf16(128, 64, false, false);
     constexpr uint32_t IDESC_PV = idesc_bf16(128, 64, false, true);
     const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aA = smem_u32(sA);
 
-    auto issue_s = [&](int t) -> bool {
-        const int e = t / g.ntiles, jt = t % g.ntiles, tile = g.t_first + jt, buf = t & 1, stage = e & 1;
-        if (jt == 0 && !mbar_wait(&bars[BAR_A_FULL + stage], (e >> 1) & 1, abort_flag)) return false;
-        if (e == 0 && !mbar_wait(&bars[BAR_KV_FULL + tile], 0, abort_flag)) return false;
+    auto issue_s = [&](int grp, int r) -> bool {
+        const int k = r / g.upe, w = r % g.upe, tile = g.t_first + (w >> 1), half = w & 1, sb = r & 1;
+        if (w == 0 && !mbar_wait(&bars[BAR_A_FULL + grp], k & 1, abort_flag)) return false;
+        if (k == 0 && half == 0 && !mbar_wait(&bars[BAR_KV_FULL + tile], 0, abort_flag)) return false;
         tc_fence_after();
+        const uint32_t kt = aK + tile * TILE_BYTES + half * 8192;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-            mma_ss(tmem + buf * 128, smem_desc_sw128(aA + stage * TILE_BYTES + 32 * k),
-                   smem_desc_sw128(aK + tile * TILE_BYTES + 32 * k), IDESC_S, k > 0);
-        tc_commit(&bars[BAR_S_FULL + buf]);
-        if (jt == g.ntiles - 1) tc_commit(&bars[BAR_A_EMPTY + stage]);
+        for (int kk = 0; kk < 4; ++kk)
+            mma_ss(tmem + grp * 128 + sb * 64, smem_desc_sw128(aA + grp * TILE_BYTES + 32 * kk),
+                   smem_desc_sw128(kt + 32 * kk), IDESC_S, kk > 0);
+        tc_commit(&bars[BAR_S_FULL + grp * 2 + sb]);
+        return true;
+    };
+    auto issue_pv = [&](int grp, int r) -> bool {
+        const int k = r / g.upe, w = r % g.upe, tile = g.t_first + (w >> 1), half = w & 1, sb = r & 1;
+        if (!mbar_wait(&bars[BAR_P_FULL + grp * 2 + sb], (r >> 1) & 1, abort_flag)) return false;
+        if (w == 0 && k >= 1 && !mbar_wait(&bars[BAR_W_EMPTY + grp], (k - 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t vt = aV + tile * TILE_BYTES + half * 8192;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+            mma_ts(tmem + 256 + grp * 64, tmem + 384 + grp * 64 + sb * 32 + 8 * kk, smem_desc_sw128(vt + 2048 * kk),
+                   IDESC_PV, (w > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&bars[BAR_PV_DONE + grp * 2 + sb]);
+        if (w == g.upe - 1) tc_commit(&bars[BAR_W_FULL + grp]);
         return true;
     };
 
-    if (!issue_s(0)) return ERR_FWD_MMA;
-    for (int t = 0; t < g.total; ++t) {
-        const int e = t / g.ntiles, jt = t % g.ntiles, tile = g.t_first + jt, buf = t & 1, wb = e & 1;
-        if (t + 1 < g.total && !issue_s(t + 1)) return ERR_FWD_MMA;
-        if (!mbar_wait(&bars[BAR_P_FULL + buf], (t >> 1) & 1, abort_flag)) return ERR_FWD_MMA;
-        if (jt == 0 && e >= 2 && !mbar_wait(&bars[BAR_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag)) return ERR_FWD_MMA;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-            mma_ts(tmem + 256 + wb * 64, tmem + buf * 128 + 8 * k, smem_desc_sw128(aV + tile * TILE_BYTES + 2048 * k),
-                   IDESC_PV, (jt > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&bars[BAR_PV_DONE + buf]);
-        if (jt == g.ntiles - 1) tc_commit(&bars[BAR_W_FULL + wb]);
+    for (int r = 0; r < 2; ++r)
+        for (int grp = 0; grp < 2; ++grp)
+            if (r < g.units[grp] && !issue_s(grp, r)) return ERR_FWD_MMA;
+    const int rounds = max(g.units[0], g.units[1]);
+    for (int r = 0; r < rounds; ++r) {
+        for (int grp = 0; grp < 2; ++grp) {
+            if (r >= g.units[grp]) continue;
+            if (!issue_pv(grp, r)) return ERR_FWD_MMA;
+            if (r + 2 < g.units[grp] && !issue_s(grp, r + 2)) return ERR_FWD_MMA;
+        }
     }
     return 0;
 }
 
-// ------------------------------------------------------------------ warps 2-5
-__device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g, uint32_t tmem, uint64_t *bars, volatile int *abort_flag) {
+// ------------------------------------------------------------------ warps 2-9
+struct RowState {
+    float ref, l;
+    float o[64];
+};
+
+// probabilities of 32 columns [col0, col0 + 32) of one S buffer -> packed bf16; returns their sum
+__device__ __forceinline__ float fwd_probs32(const uint32_t (&s)[32], uint32_t (&pk)[16], float c, float ref,
+                                             bool full, int col0, int lo, int hi) {
+    float sum0 = 0.f, sum1 = 0.f;
+    if (full) {
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+            const float p0 = ex2(fmaf(__uint_as_float(s[x]), c, -ref));
+            const float p1 = ex2(fmaf(__uint_as_float(s[x + 1]), c, -ref));
+            sum0 += p0; sum1 += p1;
+            pk[x >> 1] = pack_bf16(p0, p1);
+        }
+    } else {
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+            const int col = col0 + x;
+            float p0 = ex2(fmaf(__uint_as_float(s[x]), c, -ref));
+            float p1 = ex2(fmaf(__uint_as_float(s[x + 1]), c, -ref));
+            p0 = (col > lo && col <= hi) ? p0 : 0.f;
+            p1 = (col + 1 > lo && col + 1 <= hi) ? p1 : 0.f;
+            sum0 += p0; sum1 += p1;
+            pk[x >> 1] = pack_bf16(p0, p1);
+        }
+    }
+    return sum0 + sum1;
+}
+
+__device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g, int grp, uint32_t tmem, RowState &st,
+                                           uint8_t *sA, const uint8_t *sK2, uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = (warp & 3) * 32 + lane;            // query row within the tile = TMEM lane
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t s_addr = lane_addr + grp * 128, p_addr = lane_addr + 384 + grp * 64, w_addr = lane_addr + 256 + grp * 64;
     const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
     const int i = g.i0 + r;
     const bool row_ok = i < kp.n;
     const float c = P.c;
     const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p);
+    const int nsw = grp == 0 ? (g.nsweeps + 1) / 2 : g.nsweeps / 2;
 
-    float ref = -CUDART_INF_F, m_run = -CUDART_INF_F, l = 0.f;
-    float ref_w[2] = {-CUDART_INF_F, -CUDART_INF_F};
-    float o[64];
-#pragma unroll
-    for (int x = 0; x < 64; ++x) o[x] = 0.f;
+    float ref = -CUDART_INF_F, l = 0.f;
+    float ref_w_cur = -CUDART_INF_F, ref_w_prev = -CUDART_INF_F;
+    float (&o)[64] = st.o;
 
-    // add v2_{i-e} * W_e (TMEM) into the output registers
-    auto drain = [&](int e) -> bool {
-        const int wb = e & 1;
-        if (!warp_wait(&bars[BAR_W_FULL + wb], (e >> 1) & 1, abort_flag)) return false;
-        tc_fence_after();
+    // row r of A_e = q_i * k2_{i-e} for this group's sweep e, into the group's A stage
+    const __nv_bfloat16 *qrow = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, row_ok ? i : 0, h);
+    const bool k2_in_smem = kp.w2 <= 32;
+    auto build_a = [&](int e) {
+        uint8_t *dst = sA + (size_t)grp * TILE_BYTES;
         const int kk = i + kp.off2 - e;
-        const bool ok = row_ok && kk >= 0 && ref_w[wb] > -CUDART_INF_F;
-        const float f = ok ? ex2(ref_w[wb] - ref) : 0.f;
+        const bool ok = row_ok && kk >= 0;
+        const __nv_bfloat16 *krow = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p) + elem_off(kp.k2, b, ok ? kk : 0, hk);
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (ok) {
+                const uint4 a = *reinterpret_cast<const uint4 *>(qrow + cc * 8);
+                const uint4 kv = k2_in_smem ? *reinterpret_cast<const uint4 *>(sK2 + sw128_offset(r + 32 - e, cc))
+                                            : *reinterpret_cast<const uint4 *>(krow + cc * 8);
+                v.x = mul_bf16x2(a.x, kv.x); v.y = mul_bf16x2(a.y, kv.y);
+                v.z = mul_bf16x2(a.z, kv.z); v.w = mul_bf16x2(a.w, kv.w);
+            }
+            *reinterpret_cast<uint4 *>(dst + sw128_offset(r, cc)) = v;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars[BAR_A_FULL + grp]);
+    };
+    if (!warp_wait(&bars[BAR_K2_FULL], 0, abort_flag)) return ERR_FWD_SOFTMAX;
+    if (nsw > 0) build_a(grp);
+
+    // add v2_{i-e} * W_e (TMEM) into the output registers; ref_w is the reference W_e was built against
+    auto drain = [&](int k, float ref_w) -> bool {
+        if (!warp_wait(&bars[BAR_W_FULL + grp], k & 1, abort_flag)) return false;
+        tc_fence_after();
+        const int kk = i + kp.off2 - (2 * k + grp);
+        const bool ok = row_ok && kk >= 0 && ref_w > -CUDART_INF_F;
+        const float f = ok ? ex2(ref_w - ref) : 0.f;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             uint32_t w[32];
-            tmem_ld32(lane_addr + 256 + wb * 64 + half * 32, w);
+            tmem_ld32(w_addr + half * 32, w);
             tmem_wait_ld();
             if (ok) {
                 const __nv_bfloat16 *vp = v2 + elem_off(kp.v2, b, kk, hk) + half * 32;
@@ -250,81 +309,46 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             }
         }
         tc_fence_before();
-        mbar_arrive(&bars[BAR_W_EMPTY + wb]);
+        mbar_arrive(&bars[BAR_W_EMPTY + grp]);
         return true;
     };
 
-    for (int e = 0; e < g.nsweeps; ++e) {
+    for (int k = 0; k < nsw; ++k) {
+        const int e = 2 * k + grp;
         const bool sweep_ok = row_ok && (i + kp.off2 - e >= 0);
-        // move the reference up to the running maximum between sweeps (registers only)
-        if (m_run - ref > 8.f) {
-            const float f = ex2(ref - m_run);
-            l *= f;
-#pragma unroll
-            for (int x = 0; x < 64; ++x) o[x] *= f;
-            ref = m_run;
-        }
-        ref_w[e & 1] = ref;
-        uint32_t pmax2 = 0u;
-
-        for (int jt = 0; jt < g.ntiles; ++jt) {
-            const int t = e * g.ntiles + jt, buf = t & 1;
-            const int j0 = g.jbase + TJ * (g.t_first + jt);
+        ref_w_prev = ref_w_cur;
+        ref_w_cur = ref;
+#pragma unroll 1
+        for (int w = 0; w < g.upe; ++w) {
+            const int u = k * g.upe + w, sb = u & 1;
+            const int j0 = g.jbase + TJ * (g.t_first + (w >> 1)) + 64 * (w & 1);
             // valid columns of this row: lo < col <= hi
             const int d1 = i + kp.off1 - j0;
-            const int hi = sweep_ok ? min(d1, TJ - 1) : -1;
+            const int hi = sweep_ok ? min(d1, 63) : -1;
             const int lo = max(d1 - kp.w1, -j0 - 1);
-            if (!warp_wait(&bars[BAR_S_FULL + buf], (t >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
+            if (!warp_wait(&bars[BAR_S_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
             tc_fence_after();
-            const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= TJ - 1);
+            // every S product of this sweep has now completed: the A stage is free for the next sweep
+            if (w == g.upe - 1 && k + 1 < nsw) build_a(e + 2);
+            const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
 
-            uint32_t pp[64];
             float tile_sum = 0.f;
-            for (int pass = 0; pass < 2; ++pass) {
-                tile_sum = 0.f;
-                uint32_t tmax2 = 0u;
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t s[32];
-                    tmem_ld32(lane_addr + buf * 128 + ch * 32, s);
-                    tmem_wait_ld();
-                    if (full) {
-#pragma unroll
-                        for (int x = 0; x < 32; x += 2) {
-                            const float p0 = ex2(fmaf(__uint_as_float(s[x]), c, -ref));
-                            const float p1 = ex2(fmaf(__uint_as_float(s[x + 1]), c, -ref));
-                            tile_sum += p0 + p1;
-                            const uint32_t pk = pack_bf16(p0, p1);
-                            tmax2 = max_bf16x2(tmax2, pk);
-                            pp[ch * 16 + (x >> 1)] = pk;
-                        }
-                    } else {
-#pragma unroll
-                        for (int x = 0; x < 32; x += 2) {
-                            const int col = ch * 32 + x;
-                            float p0 = ex2(fmaf(__uint_as_float(s[x]), c, -ref));
-                            float p1 = ex2(fmaf(__uint_as_float(s[x + 1]), c, -ref));
-                            p0 = (col > lo && col <= hi) ? p0 : 0.f;
-                            p1 = (col + 1 > lo && col + 1 <= hi) ? p1 : 0.f;
-                            tile_sum += p0 + p1;
-                            const uint32_t pk = pack_bf16(p0, p1);
-                            tmax2 = max_bf16x2(tmax2, pk);
-                            pp[ch * 16 + (x >> 1)] = pk;
-                        }
-                    }
-                }
-                const float tmax = bf16x2_max_as_float(tmax2);
-                const bool exceed = !(tmax <= 1.8446744e19f);      // above 2^64, inf or NaN
-                if (pass == 1 || !__any_sync(0xffffffffu, exceed)) {
-                    pmax2 = max_bf16x2(pmax2, tmax2);
-                    break;
-                }
-                // ---- slow path (whole warp): exact tile maximum, rescale, recompute
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t s[32], pk[16];
+                tmem_ld32(s_addr + sb * 64 + ch * 32, s);
+                tmem_wait_ld();
+                tile_sum += fwd_probs32(s, pk, c, ref, full, ch * 32, lo, hi);
+                tmem_st16(p_addr + sb * 32 + ch * 16, pk);
+            }
+            const bool exceed = !(tile_sum <= 1.8446744e19f);       // above 2^64, inf or NaN
+            if (__any_sync(0xffffffffu, exceed)) {
+                // ---- slow path (whole warp): exact maximum of this unit, rescale, recompute
                 float mx = -CUDART_INF_F;
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
                     uint32_t s[32];
-                    tmem_ld32(lane_addr + buf * 128 + ch * 32, s);
+                    tmem_ld32(s_addr + sb * 64 + ch * 32, s);
                     tmem_wait_ld();
 #pragma unroll
                     for (int x = 0; x < 32; ++x) {
@@ -334,89 +358,74 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
                 }
                 float f = 1.f;
                 if (exceed) {
-                    // fold what this sweep has seen so far into the running maximum, then re-reference
-                    const float seen = bf16x2_max_as_float(pmax2);
-                    if (seen > 0.f) m_run = fmaxf(m_run, ref + lg2(seen));
                     const float nref = mx * c;
                     f = ex2(ref - nref);                       // 0 when ref was -inf
                     l *= f;
 #pragma unroll
                     for (int x = 0; x < 64; ++x) o[x] *= f;
                     ref = nref;
-                    m_run = fmaxf(m_run, nref);
-                    ref_w[e & 1] = nref;
-                    pmax2 = 0u;
+                    ref_w_cur = nref;
                 }
-                if (jt > 0) {
+                if (w > 0) {
                     // W of this sweep already holds partial sums against the old reference
-                    const int tp = t - 1;
-                    if (!warp_wait(&bars[BAR_PV_DONE + (tp & 1)], (tp >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
+                    const int up = u - 1;
+                    if (!warp_wait(&bars[BAR_PV_DONE + grp * 2 + (up & 1)], (up >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
                     tc_fence_after();
-#pragma unroll
+#pragma unroll 1
                     for (int half = 0; half < 2; ++half) {
-                        uint32_t w[32];
-                        tmem_ld32(lane_addr + 256 + (e & 1) * 64 + half * 32, w);
+                        uint32_t wv[32];
+                        tmem_ld32(w_addr + half * 32, wv);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int x = 0; x < 32; ++x) w[x] = __float_as_uint(__uint_as_float(w[x]) * f);
-                        tmem_st32(lane_addr + 256 + (e & 1) * 64 + half * 32, w);
+                        for (int x = 0; x < 32; ++x) wv[x] = __float_as_uint(__uint_as_float(wv[x]) * f);
+                        tmem_st32(w_addr + half * 32, wv);
                     }
-                    tmem_wait_st();
+                }
+                tile_sum = 0.f;
+#pragma unroll 1
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t s[32], pk[16];
+                    tmem_ld32(s_addr + sb * 64 + ch * 32, s);
+                    tmem_wait_ld();
+                    tile_sum += fwd_probs32(s, pk, c, ref, false, ch * 32, lo, hi);
+                    tmem_st16(p_addr + sb * 32 + ch * 16, pk);
                 }
             }
             l += tile_sum;
-
-            // P (bf16) over the first 64 columns of the S buffer it came from
-            {
-                uint32_t half0[32], half1[32];
-#pragma unroll
-                for (int x = 0; x < 32; ++x) { half0[x] = pp[x]; half1[x] = pp[32 + x]; }
-                tmem_st32(lane_addr + buf * 128, half0);
-                tmem_st32(lane_addr + buf * 128 + 32, half1);
-            }
             tmem_wait_st();
+            // the previous sweep's W is folded in here, where its MMAs have long finished
+            if (w == 0 && k >= 1 && !drain(k - 1, ref_w_prev)) return ERR_FWD_SOFTMAX;
             tc_fence_before();
-            mbar_arrive(&bars[BAR_P_FULL + buf]);
-
-            if (jt == 0 && e >= 1 && !drain(e - 1)) return ERR_FWD_SOFTMAX;
+            mbar_arrive(&bars[BAR_P_FULL + grp * 2 + sb]);
         }
-        const float seen = bf16x2_max_as_float(pmax2);
-        if (seen > 0.f) m_run = fmaxf(m_run, ref + lg2(seen));
     }
-    if (!drain(g.nsweeps - 1)) return ERR_FWD_SOFTMAX;
-
-    if (row_ok) {
-        const float inv = 1.f / l;
-        __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(kp.out.p) + elem_off(kp.out, b, i, h);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            uint4 v;
-            v.x = pack_bf16(o[u * 8 + 0] * inv, o[u * 8 + 1] * inv);
-            v.y = pack_bf16(o[u * 8 + 2] * inv, o[u * 8 + 3] * inv);
-            v.z = pack_bf16(o[u * 8 + 4] * inv, o[u * 8 + 5] * inv);
-            v.w = pack_bf16(o[u * 8 + 6] * inv, o[u * 8 + 7] * inv);
-            *reinterpret_cast<uint4 *>(op + u * 8) = v;
-        }
-        kp.lse[((int64_t)b * kp.hq + h) * kp.n + i] = (ref + lg2(l)) * 0.6931471805599453f;
-    }
+    if (nsw > 0 && !drain(nsw - 1, ref_w_cur)) return ERR_FWD_SOFTMAX;
+    st.ref = ref;
+    st.l = l;
     return 0;
 }
 
+__device__ __forceinline__ void fwd_groups_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+
 __global__ void __launch_bounds__(FWD_THREADS, 1)
-fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, const FwdParams P) {
+fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+           const __grid_constant__ CUtensorMap mapK2, const FwdParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sK = smem;
     uint8_t *sV = sK + (size_t)P.nt * TILE_BYTES;
     uint8_t *sA = sV + (size_t)P.nt * TILE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sA + 2 * TILE_BYTES);
+    uint8_t *sK2 = sA + 2 * TILE_BYTES;
+    float *merge_stats = reinterpret_cast<float *>(sK2 + K2_ROWS * 128);       // [2][128]: ref, l of group 1
+    uint64_t *bars = reinterpret_cast<uint64_t *>(merge_stats + 256);
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + BAR_COUNT);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
         for (int x = 0; x < BAR_COUNT; ++x) {
-            const bool many = (x >= BAR_P_FULL && x < BAR_P_FULL + 2) || (x >= BAR_W_EMPTY && x < BAR_W_EMPTY + 2);
+            const bool many = (x >= BAR_P_FULL && x < BAR_P_FULL + 4) || (x >= BAR_W_EMPTY && x < BAR_W_EMPTY + 2) ||
+                              (x >= BAR_A_FULL && x < BAR_A_FULL + 2);
             mbar_init(&bars[x], many ? 128u : 1u);
         }
         *abort_flag = 0;
@@ -434,12 +443,60 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
 
     int err = 0;
     if (warp == 0) {
-        err = fwd_producer(P, g, &mapK, &mapV, sK, sV, sA, bars, abort_flag);
+        if ((threadIdx.x & 31) == 0) fwd_producer(P, g, &mapK, &mapV, &mapK2, sK, sV, sK2, bars);
+        __syncwarp();
     } else if (warp == 1) {
         if ((threadIdx.x & 31) == 0) err = fwd_mma(P, g, tmem, sK, sV, sA, bars, abort_flag);
         __syncwarp();
     } else {
-        err = fwd_softmax(P, g, tmem, bars, abort_flag);
+        const int grp = (warp - 2) >> 2;
+        RowState st;
+#pragma unroll
+        for (int x = 0; x < 64; ++x) st.o[x] = 0.f;
+        st.ref = -CUDART_INF_F;
+        st.l = 0.f;
+        err = fwd_softmax(P, g, grp, tmem, st, sA, sK2, bars, abort_flag);
+
+        // Merge the two groups' states.  After the first barrier every MMA has completed (each
+        // group waited for its last W), so the A stages can be reused as the exchange buffer.
+        // The barriers sit outside fwd_softmax so that a group that gave up still reaches them.
+        const int r = ((warp & 3) * 32) + (threadIdx.x & 31);
+        float *xo = reinterpret_cast<float *>(sA);           // [128][64], 16-byte chunks rotated by row
+        fwd_groups_sync();
+        if (grp == 1) {
+#pragma unroll
+            for (int c4 = 0; c4 < 16; ++c4)
+                *reinterpret_cast<float4 *>(xo + r * 64 + ((c4 + r) & 15) * 4) =
+                    make_float4(st.o[c4 * 4], st.o[c4 * 4 + 1], st.o[c4 * 4 + 2], st.o[c4 * 4 + 3]);
+            merge_stats[r] = st.ref;
+            merge_stats[128 + r] = st.l;
+        }
+        fwd_groups_sync();
+        if (grp == 0) {
+            const KernelParams &kp = P.kp;
+            const int i = g.i0 + r;
+            const float ref1 = merge_stats[r], l1 = merge_stats[128 + r];
+            const float rmax = fmaxf(st.ref, ref1);
+            const float f0 = st.ref > -CUDART_INF_F ? ex2(st.ref - rmax) : 0.f;
+            const float f1 = ref1 > -CUDART_INF_F ? ex2(ref1 - rmax) : 0.f;
+            const float l = st.l * f0 + l1 * f1;
+            if (i < kp.n && err == 0) {
+                const float inv = 1.f / l;
+                __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(kp.out.p) + elem_off(kp.out, blockIdx.z, i, blockIdx.y);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float4 a = *reinterpret_cast<const float4 *>(xo + r * 64 + ((2 * u + r) & 15) * 4);
+                    const float4 bq = *reinterpret_cast<const float4 *>(xo + r * 64 + ((2 * u + 1 + r) & 15) * 4);
+                    uint4 v;
+                    v.x = pack_bf16((st.o[u * 8 + 0] * f0 + a.x * f1) * inv, (st.o[u * 8 + 1] * f0 + a.y * f1) * inv);
+                    v.y = pack_bf16((st.o[u * 8 + 2] * f0 + a.z * f1) * inv, (st.o[u * 8 + 3] * f0 + a.w * f1) * inv);
+                    v.z = pack_bf16((st.o[u * 8 + 4] * f0 + bq.x * f1) * inv, (st.o[u * 8 + 5] * f0 + bq.y * f1) * inv);
+                    v.w = pack_bf16((st.o[u * 8 + 6] * f0 + bq.z * f1) * inv, (st.o[u * 8 + 7] * f0 + bq.w * f1) * inv);
+                    *reinterpret_cast<uint4 *>(op + u * 8) = v;
+                }
+                kp.lse[((int64_t)blockIdx.z * kp.hq + blockIdx.y) * kp.n + i] = (rmax + lg2(l)) * 0.6931471805599453f;
+            }
+        }
     }
     if (err) atomicOr(P.status, err);
 
