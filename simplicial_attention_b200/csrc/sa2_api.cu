@@ -83,6 +83,13 @@ extern "C" {
 
 int sa2_version(void) { return 100; }
 
+#ifdef SA2_TRACE
+// diagnostic builds only: copy the timeline stamps of the traced forward CTA to the host
+int sa2_trace_read(unsigned long long *host, int n) {
+    return cudaMemcpyFromSymbol(host, sa2::tc::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
+}
+#endif
+
 int sa2_device_status(int reset) {
     int *word = sa2::tc::status_word();
     if (!word) return -1;

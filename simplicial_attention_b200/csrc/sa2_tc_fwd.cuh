@@ -13,16 +13,17 @@
 //
 // Warp roles (320 threads):
 //   warp 0      TMA producer: the K1/V1 window and the 127 + 32 second-key rows
-//               the tile can pair with, loaded once and resident in shared memory
-//   warp 1      issues every tcgen05.mma (one lane), owns the TMEM allocation
+//               the tile can pair with, loaded once and resident in shared memory;
+//               then issues the tcgen05.mma stream of group 1 (one lane)
+//   warp 1      owns the TMEM allocation, issues the tcgen05.mma stream of group 0
 //   warps 2-5   softmax group 0: even sweeps, one thread per query row
 //   warps 6-9   softmax group 1: odd sweeps, one thread per query row
 // A group builds the A tile of its next sweep itself (row r by the thread that
 // owns row r) as soon as the last S product of its current sweep has completed,
 // so the tile is ready long before the tensor cores need it.
-// The MMA warp interleaves the tiles of an even and an odd sweep, so while one
-// group runs the exponentials of its tile the tensor cores work for the other
-// and each SM sub-partition has two softmax warps to hide latencies.  Every
+// An even and an odd sweep are in flight together, so while one group runs the
+// exponentials of its tile the tensor cores work for the other and each SM
+// sub-partition has two softmax warps to hide latencies.  Every
 // group keeps its own (reference, denominator, output) state per row; the two
 // states are merged through shared memory at the end.
 //
@@ -85,6 +86,17 @@ inline size_t fwd_smem_bytes(int nt) {
     const size_t need = 1024 + (size_t)nt * 2 * TILE_BYTES + 2 * TILE_BYTES + K2_ROWS * 128 + 256 + 1024;
     return need > 120 * 1024 ? need : 120 * 1024;
 }
+
+// Optional timeline of one CTA (compile with -DSA2_TRACE): clock64 stamps at the pipeline's hand-over points.
+#ifdef SA2_TRACE
+__device__ unsigned long long g_trace[8192];
+__device__ __forceinline__ void trace_mark(int slot) {
+    if (blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && slot < 8192) g_trace[slot] = clock64();
+}
+#define SA2_TRACE_MARK(cond, slot) do { if (cond) trace_mark(slot); } while (0)
+#else
+#define SA2_TRACE_MARK(cond, slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -153,52 +165,65 @@ __device__ __forceinline__ void fwd_producer(const FwdParams &P, const FwdGeom &
     }
 }
 
-// ------------------------------------------------------------------ warp 1 (one lane)
+// ------------------------------------------------------------------ MMA issuers (one lane each)
+// Lane 0 of warp 1 issues for group 0 and lane 0 of warp 0 for group 1: the two groups touch disjoint
+// TMEM columns and only read shared memory, so their MMA streams need no ordering between them, and
+// two issuing threads double the rate at which instructions reach the tensor cores.
 // Group g's stream: unit r is half tile r % upe of the group's (r / upe)-th sweep, e = 2 (r / upe) + g.
-__device__ __forceinline__ int fwd_mma(const FwdParams &P, const FwdGeom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sA,
+__device__ __forceinline__ int fwd_mma(const FwdGeom &g, int grp, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sA,
                                        uint64_t *bars, volatile int *abort_flag) {
     constexpr uint32_t IDESC_S = idesc_bf16(128, 64, false, false);
     constexpr uint32_t IDESC_PV = idesc_bf16(128, 64, false, true);
-    const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aA = smem_u32(sA);
+    // descriptors differ only in their start-address field (units of 16 bytes): build them once
+    const uint64_t dA = smem_desc_sw128(smem_u32(sA) + grp * TILE_BYTES);
+    const uint64_t dK = smem_desc_sw128(smem_u32(sK));
+    const uint64_t dV = smem_desc_sw128(smem_u32(sV));
+    const uint32_t tS = tmem + grp * 128, tW = tmem + 256 + grp * 64, tP = tmem + 384 + grp * 64;
+    const int n = g.units[grp];
 
-    auto issue_s = [&](int grp, int r) -> bool {
-        const int k = r / g.upe, w = r % g.upe, tile = g.t_first + (w >> 1), half = w & 1, sb = r & 1;
-        if (w == 0 && !mbar_wait(&bars[BAR_A_FULL + grp], k & 1, abort_flag)) return false;
-        if (k == 0 && half == 0 && !mbar_wait(&bars[BAR_KV_FULL + tile], 0, abort_flag)) return false;
+    // running position of the unit whose S is issued next (s_*) and whose PV is issued next (p_*)
+    int s_k = 0, s_w = 0, p_k = 0, p_w = 0;
+
+    auto issue_s = [&](int r) -> bool {
+        const int tile = g.t_first + (s_w >> 1), half = s_w & 1, sb = r & 1;
+        if (s_w == 0 && !mbar_wait(&bars[BAR_A_FULL + grp], s_k & 1, abort_flag)) return false;
+        if (s_k == 0 && half == 0 && !mbar_wait(&bars[BAR_KV_FULL + tile], 0, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t kt = aK + tile * TILE_BYTES + half * 8192;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-            mma_ss(tmem + grp * 128 + sb * 64, smem_desc_sw128(aA + grp * TILE_BYTES + 32 * kk),
-                   smem_desc_sw128(kt + 32 * kk), IDESC_S, kk > 0);
+        const uint64_t kt = dK + (uint64_t)((tile * TILE_BYTES + half * 8192) >> 4);
+        const uint32_t d = tS + sb * 64;
+        mma_ss(d, dA, kt, IDESC_S, 0u);
+        mma_ss(d, dA + 2, kt + 2, IDESC_S, 1u);
+        mma_ss(d, dA + 4, kt + 4, IDESC_S, 1u);
+        mma_ss(d, dA + 6, kt + 6, IDESC_S, 1u);
         tc_commit(&bars[BAR_S_FULL + grp * 2 + sb]);
+        if (++s_w == g.upe) { s_w = 0; ++s_k; }
         return true;
     };
-    auto issue_pv = [&](int grp, int r) -> bool {
-        const int k = r / g.upe, w = r % g.upe, tile = g.t_first + (w >> 1), half = w & 1, sb = r & 1;
+    auto issue_pv = [&](int r) -> bool {
+        const int tile = g.t_first + (p_w >> 1), half = p_w & 1, sb = r & 1;
+        SA2_TRACE_MARK(true, 4096 + (grp * 160 + r) * 4);
         if (!mbar_wait(&bars[BAR_P_FULL + grp * 2 + sb], (r >> 1) & 1, abort_flag)) return false;
-        if (w == 0 && k >= 1 && !mbar_wait(&bars[BAR_W_EMPTY + grp], (k - 1) & 1, abort_flag)) return false;
+        SA2_TRACE_MARK(true, 4096 + (grp * 160 + r) * 4 + 1);
+        if (p_w == 0 && p_k >= 1 && !mbar_wait(&bars[BAR_W_EMPTY + grp], (p_k - 1) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t vt = aV + tile * TILE_BYTES + half * 8192;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-            mma_ts(tmem + 256 + grp * 64, tmem + 384 + grp * 64 + sb * 32 + 8 * kk, smem_desc_sw128(vt + 2048 * kk),
-                   IDESC_PV, (w > 0 || kk > 0) ? 1u : 0u);
+        const uint64_t vt = dV + (uint64_t)((tile * TILE_BYTES + half * 8192) >> 4);
+        const uint32_t a = tP + sb * 32;
+        mma_ts(tW, a, vt, IDESC_PV, p_w > 0 ? 1u : 0u);
+        mma_ts(tW, a + 8, vt + 128, IDESC_PV, 1u);
+        mma_ts(tW, a + 16, vt + 256, IDESC_PV, 1u);
+        mma_ts(tW, a + 24, vt + 384, IDESC_PV, 1u);
         tc_commit(&bars[BAR_PV_DONE + grp * 2 + sb]);
-        if (w == g.upe - 1) tc_commit(&bars[BAR_W_FULL + grp]);
+        if (p_w == g.upe - 1) tc_commit(&bars[BAR_W_FULL + grp]);
+        SA2_TRACE_MARK(true, 4096 + (grp * 160 + r) * 4 + 2);
+        if (++p_w == g.upe) { p_w = 0; ++p_k; }
         return true;
     };
 
-    for (int r = 0; r < 2; ++r)
-        for (int grp = 0; grp < 2; ++grp)
-            if (r < g.units[grp] && !issue_s(grp, r)) return ERR_FWD_MMA;
-    const int rounds = max(g.units[0], g.units[1]);
-    for (int r = 0; r < rounds; ++r) {
-        for (int grp = 0; grp < 2; ++grp) {
-            if (r >= g.units[grp]) continue;
-            if (!issue_pv(grp, r)) return ERR_FWD_MMA;
-            if (r + 2 < g.units[grp] && !issue_s(grp, r + 2)) return ERR_FWD_MMA;
-        }
+    for (int r = 0; r < 2 && r < n; ++r)
+        if (!issue_s(r)) return ERR_FWD_MMA;
+    for (int r = 0; r < n; ++r) {
+        if (!issue_pv(r)) return ERR_FWD_MMA;
+        if (r + 2 < n && !issue_s(r + 2)) return ERR_FWD_MMA;
     }
     return 0;
 }
@@ -326,7 +351,9 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             const int d1 = i + kp.off1 - j0;
             const int hi = sweep_ok ? min(d1, 63) : -1;
             const int lo = max(d1 - kp.w1, -j0 - 1);
+            SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4);
             if (!warp_wait(&bars[BAR_S_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
+            SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 1);
             tc_fence_after();
             // every S product of this sweep has now completed: the A stage is free for the next sweep
             if (w == g.upe - 1 && k + 1 < nsw) build_a(e + 2);
@@ -393,10 +420,12 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             }
             l += tile_sum;
             tmem_wait_st();
+            SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 2);
             // the previous sweep's W is folded in here, where its MMAs have long finished
             if (w == 0 && k >= 1 && !drain(k - 1, ref_w_prev)) return ERR_FWD_SOFTMAX;
             tc_fence_before();
             mbar_arrive(&bars[BAR_P_FULL + grp * 2 + sb]);
+            SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 3);
         }
     }
     if (nsw > 0 && !drain(nsw - 1, ref_w_cur)) return ERR_FWD_SOFTMAX;
@@ -443,10 +472,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
 
     int err = 0;
     if (warp == 0) {
-        if ((threadIdx.x & 31) == 0) fwd_producer(P, g, &mapK, &mapV, &mapK2, sK, sV, sK2, bars);
+        if ((threadIdx.x & 31) == 0) {
+            fwd_producer(P, g, &mapK, &mapV, &mapK2, sK, sV, sK2, bars);
+            err = fwd_mma(g, 1, tmem, sK, sV, sA, bars, abort_flag);
+        }
         __syncwarp();
     } else if (warp == 1) {
-        if ((threadIdx.x & 31) == 0) err = fwd_mma(P, g, tmem, sK, sV, sA, bars, abort_flag);
+        if ((threadIdx.x & 31) == 0) err = fwd_mma(g, 0, tmem, sK, sV, sA, bars, abort_flag);
         __syncwarp();
     } else {
         const int grp = (warp - 2) >> 2;
