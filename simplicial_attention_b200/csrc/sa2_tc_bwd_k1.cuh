@@ -16,16 +16,22 @@
 // The same shared-memory tile is the K-major B operand of the first product
 // and the MN-major B operand of the second.
 //
-// Warps (320 threads): 0 TMA producer, 1 MMA issuer + TMEM owner, 2-5 compute,
-// 6-9 builders.  TMEM columns: half h -> [128h, 128h+64) S^T then P^T,
-// [128h+64, 128h+128) dP^T then G^T; dK1 [256,320); dV1 [320,384).
+// Warps (448 threads): 0 TMA producer, then issuer of the second products (dV1, dK1);
+// 1 TMEM owner and issuer of the first products (S^T, dP^T); 2-5 compute group of
+// half 0; 6-9 compute group of half 1; 10-13 builders.  One thread issues about one
+// tcgen05.mma per 90 cycles, so the two products have an issuing thread each; dK1/dV1
+// are accumulated by one thread only, which keeps the summation order fixed.
+// TMEM columns: half h -> S^T [128h, +64), dP^T [128h+64, +64), P^T (bf16) [256+64h, +32),
+// G^T (bf16) [288+64h, +32); dK1 [384,448); dV1 [448,512).  P^T/G^T have their own
+// columns so that the next S^T/dP^T of a half can be issued as soon as the compute
+// group has read the current one.
 #pragma once
 #include "sa2_tc_fwd.cuh"
 
 namespace sa2 {
 namespace tc {
 
-constexpr int BK1_THREADS = 320;
+constexpr int BK1_THREADS = 448;
 
 enum Bk1Bar {
     BK1_KV_FULL = 0,
@@ -33,8 +39,9 @@ enum Bk1Bar {
     BK1_AB_EMPTY = 3,    // [2]
     BK1_S_FULL = 5,      // [2] per half
     BK1_P_FULL = 7,      // [2] per half
-    BK1_DONE = 9,
-    BK1_BAR_COUNT = 10
+    BK1_G_DONE = 9,      // [2] per half: second products of the step have completed
+    BK1_DONE = 11,
+    BK1_BAR_COUNT = 12
 };
 
 enum { ERR_BK1_PRODUCER = 16, ERR_BK1_MMA = 32, ERR_BK1_COMPUTE = 64, ERR_BK1_BUILDER = 128 };
@@ -69,11 +76,11 @@ __device__ __forceinline__ Bk1Geom bk1_geom(const KernelParams &kp) {
     return g;
 }
 
-// ---------------------------------------------------------------- builders (warps 6-9)
+// ---------------------------------------------------------------- builders (warps 10-13)
 __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g, uint8_t *sAB, float *stats,
                                            uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
-    const int r = threadIdx.x - 192;       // row of the query tile
+    const int r = threadIdx.x - 320;       // row of the query tile
     const int hk = blockIdx.y, b = blockIdx.z;
     const __nv_bfloat16 *q = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p);
     const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
@@ -104,7 +111,9 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
             }
             for (int e = 0; e < ne; ++e, ++s) {
                 const int stage = s & 1;
+                SA2_TRACE_MARK(r == 0 && s < 200, s * 4);
                 if (s >= 2 && !warp_wait(&bars[BK1_AB_EMPTY + stage], ((s >> 1) - 1) & 1, abort_flag)) return ERR_BK1_BUILDER;
+                SA2_TRACE_MARK(r == 0 && s < 200, s * 4 + 1);
                 if (e == 0) {
                     // column statistics of this query tile; the buffer of two tiles ago is no longer read
                     float *st = stats + (tile_counter & 1) * 256;
@@ -133,67 +142,87 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&bars[BK1_AB_FULL + stage]);
+                SA2_TRACE_MARK(r == 0 && s < 200, s * 4 + 2);
             }
         }
     }
     return 0;
 }
 
-// ---------------------------------------------------------------- MMA issuer (warp 1, one lane)
-__device__ __forceinline__ int bk1_mma(const Bk1Geom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sAB,
-                                       uint64_t *bars, volatile int *abort_flag) {
-    constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);   // S^T, dP^T halves
-    constexpr uint32_t IDESC_G = idesc_bf16(128, 64, false, true);    // dV, dK (B operand MN-major)
-    const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aAB = smem_u32(sAB);
-
-    auto first = [&](int s, int half) -> bool {
-        const int stage = s & 1;
-        if (half == 0 && !mbar_wait(&bars[BK1_AB_FULL + stage], (s >> 1) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t aA = aAB + stage * 2 * TILE_BYTES + half * 8192, aB = aA + TILE_BYTES;
-        const uint32_t d = tmem + half * 128;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(d, smem_desc_sw128(aK + 32 * k), smem_desc_sw128(aA + 32 * k), IDESC_F, k > 0);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(d + 64, smem_desc_sw128(aV + 32 * k), smem_desc_sw128(aB + 32 * k), IDESC_F, k > 0);
-        tc_commit(&bars[BK1_S_FULL + half]);
-        return true;
-    };
-    auto second = [&](int s, int half) -> bool {
-        const int stage = s & 1;
-        if (!mbar_wait(&bars[BK1_P_FULL + half], s & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t aA = aAB + stage * 2 * TILE_BYTES + half * 8192, aB = aA + TILE_BYTES;
-        const uint32_t a = tmem + half * 128;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-            mma_ts(tmem + 320, a + 8 * k, smem_desc_sw128(aB + 2048 * k), IDESC_G, (s > 0 || half > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-            mma_ts(tmem + 256, a + 64 + 8 * k, smem_desc_sw128(aA + 2048 * k), IDESC_G, (s > 0 || half > 0 || k > 0) ? 1u : 0u);
-        return true;
-    };
-
+// ---------------------------------------------------------------- issuer of S^T, dP^T (warp 1, one lane)
+__device__ __forceinline__ int bk1_mma_first(const Bk1Geom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sAB,
+                                             uint64_t *bars, volatile int *abort_flag) {
+    constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);
+    const uint64_t dK = smem_desc_sw128(smem_u32(sK)), dV = smem_desc_sw128(smem_u32(sV));
+    const uint64_t dAB = smem_desc_sw128(smem_u32(sAB));
     if (!mbar_wait(&bars[BK1_KV_FULL], 0, abort_flag)) return ERR_BK1_MMA;
-    if (!first(0, 0) || !first(0, 1)) return ERR_BK1_MMA;
     for (int s = 0; s < g.total; ++s) {
-        if (!second(s, 0)) return ERR_BK1_MMA;
-        if (s + 1 < g.total && !first(s + 1, 0)) return ERR_BK1_MMA;
-        if (!second(s, 1)) return ERR_BK1_MMA;
-        tc_commit(&bars[BK1_AB_EMPTY + (s & 1)]);
-        if (s + 1 < g.total && !first(s + 1, 1)) return ERR_BK1_MMA;
+        const int stage = s & 1;
+        if (!mbar_wait(&bars[BK1_AB_FULL + stage], (s >> 1) & 1, abort_flag)) return ERR_BK1_MMA;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            // the compute group must have read the previous step's S^T / dP^T of this half
+            SA2_TRACE_MARK(s < 200, 1000 + (s * 2 + half) * 4);
+            if (s >= 1 && !mbar_wait(&bars[BK1_P_FULL + half], (s - 1) & 1, abort_flag)) return ERR_BK1_MMA;
+            SA2_TRACE_MARK(s < 200, 1000 + (s * 2 + half) * 4 + 1);
+            tc_fence_after();
+            const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4), bq = a + (TILE_BYTES >> 4);
+            const uint32_t d = tmem + half * 128;
+            mma_ss(d, dK, a, IDESC_F, 0u);
+            mma_ss(d, dK + 2, a + 2, IDESC_F, 1u);
+            mma_ss(d, dK + 4, a + 4, IDESC_F, 1u);
+            mma_ss(d, dK + 6, a + 6, IDESC_F, 1u);
+            mma_ss(d + 64, dV, bq, IDESC_F, 0u);
+            mma_ss(d + 64, dV + 2, bq + 2, IDESC_F, 1u);
+            mma_ss(d + 64, dV + 4, bq + 4, IDESC_F, 1u);
+            mma_ss(d + 64, dV + 6, bq + 6, IDESC_F, 1u);
+            tc_commit(&bars[BK1_S_FULL + half]);
+            SA2_TRACE_MARK(s < 200, 1000 + (s * 2 + half) * 4 + 2);
+        }
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------- issuer of dV1, dK1 (warp 0, one lane)
+__device__ __forceinline__ int bk1_mma_second(const Bk1Geom &g, uint32_t tmem, uint8_t *sAB, uint64_t *bars, volatile int *abort_flag) {
+    constexpr uint32_t IDESC_G = idesc_bf16(128, 64, false, true);    // B operand MN-major
+    const uint64_t dAB = smem_desc_sw128(smem_u32(sAB));
+    for (int s = 0; s < g.total; ++s) {
+        const int stage = s & 1;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            SA2_TRACE_MARK(s < 200, 3000 + (s * 2 + half) * 4);
+            if (!mbar_wait(&bars[BK1_P_FULL + half], s & 1, abort_flag)) return ERR_BK1_MMA;
+            SA2_TRACE_MARK(s < 200, 3000 + (s * 2 + half) * 4 + 1);
+            tc_fence_after();
+            const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4), bq = a + (TILE_BYTES >> 4);
+            const uint32_t t = tmem + 256 + half * 64;
+            const uint32_t first = (s > 0 || half > 0) ? 1u : 0u;
+            mma_ts(tmem + 448, t, bq, IDESC_G, first);
+            mma_ts(tmem + 448, t + 8, bq + 128, IDESC_G, 1u);
+            mma_ts(tmem + 448, t + 16, bq + 256, IDESC_G, 1u);
+            mma_ts(tmem + 448, t + 24, bq + 384, IDESC_G, 1u);
+            mma_ts(tmem + 384, t + 32, a, IDESC_G, first);
+            mma_ts(tmem + 384, t + 40, a + 128, IDESC_G, 1u);
+            mma_ts(tmem + 384, t + 48, a + 256, IDESC_G, 1u);
+            mma_ts(tmem + 384, t + 56, a + 384, IDESC_G, 1u);
+            tc_commit(&bars[BK1_G_DONE + half]);
+            SA2_TRACE_MARK(s < 200, 3000 + (s * 2 + half) * 4 + 2);
+        }
+        tc_commit(&bars[BK1_AB_EMPTY + stage]);
     }
     tc_commit(&bars[BK1_DONE]);
     return 0;
 }
 
-// ---------------------------------------------------------------- compute (warps 2-5)
-__device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g, uint32_t tmem, const float *stats,
+// ---------------------------------------------------------------- compute (group h = half h: warps 2-5, 6-9)
+__device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g, int half, uint32_t tmem, const float *stats,
                                            uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = (warp & 3) * 32 + lane;          // key row within the tile = TMEM lane
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t buf = lane_addr + half * 128, pg = lane_addr + 256 + half * 64;
     const int hk = blockIdx.y, b = blockIdx.z;
     const int j = g.j0 + r;
     const bool jv = j < kp.nk1;
@@ -204,82 +233,89 @@ __device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g,
         for (int t = 0; t < g.n_it; ++t, ++tile_counter) {
             const int it0 = g.i_lo + TQ * t;
             const int ne = bk1_sweeps(kp, g, t);
-            const float *st = stats + (tile_counter & 1) * 256;
+            const float *st = stats + (tile_counter & 1) * 256 + half * 64;
             const int base = j - kp.off1 - it0;                       // column of the diagonal i + off1 == j
-            const int hi_all = jv ? min(min(TQ - 1, base + kp.w1 - 1), g.i_hi - it0) : -1;
+            const int hi = (jv ? min(min(TQ - 1, base + kp.w1 - 1), g.i_hi - it0) : -1) - half * 64;
             for (int e = 0; e < ne; ++e, ++s) {
                 // the builders' statistics (written before they signalled this stage) must be visible
                 if (e == 0 && !warp_wait(&bars[BK1_AB_FULL + (s & 1)], (s >> 1) & 1, abort_flag)) return ERR_BK1_COMPUTE;
-                const int lo_all = max(max(0, base), e - kp.off2 - it0);
-#pragma unroll 1
-                for (int half = 0; half < 2; ++half) {
-                    if (!warp_wait(&bars[BK1_S_FULL + half], s & 1, abort_flag)) return ERR_BK1_COMPUTE;
-                    tc_fence_after();
-                    const int lo = lo_all - half * 64, hi = hi_all - half * 64;     // valid columns: lo <= col <= hi
-                    const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
-                    uint32_t pp[32], gg[32];
+                const int lo = max(max(0, base), e - kp.off2 - it0) - half * 64;     // valid columns: lo <= col <= hi
+                SA2_TRACE_MARK(r == 0 && s < 200, 5000 + (s * 2 + half) * 4);
+                if (!warp_wait(&bars[BK1_S_FULL + half], s & 1, abort_flag)) return ERR_BK1_COMPUTE;
+                SA2_TRACE_MARK(r == 0 && s < 200, 5000 + (s * 2 + half) * 4 + 1);
+                tc_fence_after();
+                const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
+                // P^T / G^T of the previous step must have been consumed before they are overwritten
+                if (s >= 1 && !warp_wait(&bars[BK1_G_DONE + half], (s - 1) & 1, abort_flag)) return ERR_BK1_COMPUTE;
 #pragma unroll
-                    for (int ch = 0; ch < 2; ++ch) {
-                        uint32_t sv[32], dv[32];
-                        tmem_ld32(lane_addr + half * 128 + ch * 32, sv);
-                        tmem_ld32(lane_addr + half * 128 + 64 + ch * 32, dv);
-                        tmem_wait_ld();
-                        const float4 *l4 = reinterpret_cast<const float4 *>(st + half * 64 + ch * 32);
-                        const float4 *d4 = reinterpret_cast<const float4 *>(st + 128 + half * 64 + ch * 32);
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t sv[32], dv[32], pk[16], gk[16];
+                    tmem_ld32(buf + ch * 32, sv);
+                    tmem_ld32(buf + 64 + ch * 32, dv);
+                    tmem_wait_ld();
+                    const float4 *l4 = reinterpret_cast<const float4 *>(st + ch * 32);
+                    const float4 *d4 = reinterpret_cast<const float4 *>(st + 128 + ch * 32);
+                    if (full) {
 #pragma unroll
                         for (int x4 = 0; x4 < 8; ++x4) {
                             const float4 lv = l4[x4], dl = d4[x4];
-                            const float ls[4] = {lv.x, lv.y, lv.z, lv.w};
-                            const float ds[4] = {dl.x, dl.y, dl.z, dl.w};
-                            float p[4], gq[4];
+                            const float p0 = ex2(fmaf(__uint_as_float(sv[x4 * 4]), c, -lv.x));
+                            const float p1 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 1]), c, -lv.y));
+                            const float p2 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 2]), c, -lv.z));
+                            const float p3 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 3]), c, -lv.w));
+                            pk[x4 * 2] = pack_bf16(p0, p1);
+                            pk[x4 * 2 + 1] = pack_bf16(p2, p3);
+                            gk[x4 * 2] = pack_bf16(p0 * (__uint_as_float(dv[x4 * 4]) - dl.x), p1 * (__uint_as_float(dv[x4 * 4 + 1]) - dl.y));
+                            gk[x4 * 2 + 1] = pack_bf16(p2 * (__uint_as_float(dv[x4 * 4 + 2]) - dl.z), p3 * (__uint_as_float(dv[x4 * 4 + 3]) - dl.w));
+                        }
+                    } else {
 #pragma unroll
-                            for (int z = 0; z < 4; ++z) {
-                                const int x = x4 * 4 + z;
-                                float pv = ex2(fmaf(__uint_as_float(sv[x]), c, -ls[z]));
-                                if (!full) {
-                                    const int col = ch * 32 + x;
-                                    pv = (col >= lo && col <= hi) ? pv : 0.f;
-                                }
-                                p[z] = pv;
-                                gq[z] = pv * (__uint_as_float(dv[x]) - ds[z]);
-                            }
-                            pp[ch * 16 + x4 * 2] = pack_bf16(p[0], p[1]);
-                            pp[ch * 16 + x4 * 2 + 1] = pack_bf16(p[2], p[3]);
-                            gg[ch * 16 + x4 * 2] = pack_bf16(gq[0], gq[1]);
-                            gg[ch * 16 + x4 * 2 + 1] = pack_bf16(gq[2], gq[3]);
+                        for (int x4 = 0; x4 < 8; ++x4) {
+                            const float4 lv = l4[x4], dl = d4[x4];
+                            const int col = ch * 32 + x4 * 4;
+                            float p0 = ex2(fmaf(__uint_as_float(sv[x4 * 4]), c, -lv.x));
+                            float p1 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 1]), c, -lv.y));
+                            float p2 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 2]), c, -lv.z));
+                            float p3 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 3]), c, -lv.w));
+                            p0 = (col >= lo && col <= hi) ? p0 : 0.f;
+                            p1 = (col + 1 >= lo && col + 1 <= hi) ? p1 : 0.f;
+                            p2 = (col + 2 >= lo && col + 2 <= hi) ? p2 : 0.f;
+                            p3 = (col + 3 >= lo && col + 3 <= hi) ? p3 : 0.f;
+                            pk[x4 * 2] = pack_bf16(p0, p1);
+                            pk[x4 * 2 + 1] = pack_bf16(p2, p3);
+                            gk[x4 * 2] = pack_bf16(p0 * (__uint_as_float(dv[x4 * 4]) - dl.x), p1 * (__uint_as_float(dv[x4 * 4 + 1]) - dl.y));
+                            gk[x4 * 2 + 1] = pack_bf16(p2 * (__uint_as_float(dv[x4 * 4 + 2]) - dl.z), p3 * (__uint_as_float(dv[x4 * 4 + 3]) - dl.w));
                         }
                     }
-                    tmem_st32(lane_addr + half * 128, pp);
-                    tmem_st32(lane_addr + half * 128 + 64, gg);
-                    tmem_wait_st();
-                    tc_fence_before();
-                    mbar_arrive(&bars[BK1_P_FULL + half]);
+                    tmem_st16(pg + ch * 16, pk);
+                    tmem_st16(pg + 32 + ch * 16, gk);
                 }
+                tmem_wait_st();
+                SA2_TRACE_MARK(r == 0 && s < 200, 5000 + (s * 2 + half) * 4 + 2);
+                tc_fence_before();
+                mbar_arrive(&bars[BK1_P_FULL + half]);
             }
         }
     }
-    // drain dK1, dV1
+    // drain: group 0 writes dK1, group 1 writes dV1
     if (!warp_wait(&bars[BK1_DONE], 0, abort_flag)) return ERR_BK1_COMPUTE;
     tc_fence_after();
     const bool gbf16 = kp.grad_bf16 != 0;
+    const TensorRef &dst = half == 0 ? kp.dk1 : kp.dv1;
+    const float mul = half == 0 ? kp.scale : 1.f;
 #pragma unroll 1
-    for (int which = 0; which < 2; ++which) {
-        const TensorRef &dst = which == 0 ? kp.dk1 : kp.dv1;
-        const float mul = which == 0 ? kp.scale : 1.f;
-#pragma unroll 1
-        for (int hf = 0; hf < 2; ++hf) {
-            uint32_t w[32];
-            tmem_ld32(lane_addr + 256 + which * 64 + hf * 32, w);
-            tmem_wait_ld();
-            if (jv) {
-                const int64_t off = elem_off(dst, b, j, hk) + hf * 32;
+    for (int hf = 0; hf < 2; ++hf) {
+        uint32_t w[32];
+        tmem_ld32(lane_addr + 384 + half * 64 + hf * 32, w);
+        tmem_wait_ld();
+        if (jv) {
+            const int64_t off = elem_off(dst, b, j, hk) + hf * 32;
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    float x[4];
+            for (int u = 0; u < 8; ++u) {
+                float x[4];
 #pragma unroll
-                    for (int z = 0; z < 4; ++z) x[z] = (g.total > 0 ? __uint_as_float(w[u * 4 + z]) : 0.f) * mul;
-                    store_vec<4>(dst.p, off + u * 4, gbf16, x);
-                }
+                for (int z = 0; z < 4; ++z) x[z] = (g.total > 0 ? __uint_as_float(w[u * 4 + z]) : 0.f) * mul;
+                store_vec<4>(dst.p, off + u * 4, gbf16, x);
             }
         }
     }
@@ -319,24 +355,26 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
 
     int err = 0;
     if (warp == 0) {
-        if (lane == 0 && g.total > 0) {
-            prefetch_tmap(&mapK);
-            prefetch_tmap(&mapV);
-            mbar_arrive_expect_tx(&bars[BK1_KV_FULL], 2 * TILE_BYTES);
-            tma_load_4d(sK, &mapK, &bars[BK1_KV_FULL], 0, blockIdx.y, g.j0, blockIdx.z);
-            tma_load_4d(sV, &mapV, &bars[BK1_KV_FULL], 0, blockIdx.y, g.j0, blockIdx.z);
-            // the tile must have landed before the CTA may exit, even if every other role gave up
-            if (!mbar_wait(&bars[BK1_KV_FULL], 0, abort_flag)) err = ERR_BK1_PRODUCER;
+        if (lane == 0) {
+            if (g.total > 0) {
+                prefetch_tmap(&mapK);
+                prefetch_tmap(&mapV);
+                mbar_arrive_expect_tx(&bars[BK1_KV_FULL], 2 * TILE_BYTES);
+                tma_load_4d(sK, &mapK, &bars[BK1_KV_FULL], 0, blockIdx.y, g.j0, blockIdx.z);
+                tma_load_4d(sV, &mapV, &bars[BK1_KV_FULL], 0, blockIdx.y, g.j0, blockIdx.z);
+                err = bk1_mma_second(g, tmem, sAB, bars, abort_flag);
+                // the tile must have landed before the CTA may exit, even if every other role gave up
+                if (!mbar_wait(&bars[BK1_KV_FULL], 0, abort_flag)) err |= ERR_BK1_PRODUCER;
+            } else {
+                tc_commit(&bars[BK1_DONE]);
+            }
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
-            if (g.total > 0) err = bk1_mma(g, tmem, sK, sV, sAB, bars, abort_flag);
-            else tc_commit(&bars[BK1_DONE]);
-        }
+        if (lane == 0 && g.total > 0) err = bk1_mma_first(g, tmem, sK, sV, sAB, bars, abort_flag);
         __syncwarp();
-    } else if (warp < 6) {
-        err = bk1_compute(P, g, tmem, stats, bars, abort_flag);
+    } else if (warp < 10) {
+        err = bk1_compute(P, g, (warp - 2) >> 2, tmem, stats, bars, abort_flag);
     } else {
         err = bk1_builder(P, g, sAB, stats, bars, abort_flag);
     }
