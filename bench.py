@@ -187,6 +187,9 @@ def main():
     ap.add_argument("--workload", default="C3", choices=sorted(WORKLOADS))
     ap.add_argument("--kernel", default="auto", choices=("auto", "simt", "tcgen05"))
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--sharding", default="batch", choices=("batch", "seq"),
+                    help="batch: every rank runs its own batch (no collective); seq: the ranks hold consecutive blocks "
+                         "of one sequence of length n * N and exchange the key/value halo over NCCL")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
     args = ap.parse_args()
@@ -214,9 +217,24 @@ def main():
     q, k1, k2, v1, v2, do = devt
     w1, w2 = cfg["w1"], cfg["w2"]
     fl = work_flops(cfg)
+    seq = args.sharding == "seq" and world > 1
+    if seq:
+        # one sequence of length n * world: per-rank share of its unmasked triples
+        whole = dict(cfg, n=cfg["n"] * world)
+        fl = {k: v / world for k, v in work_flops(whole).items()}
+        from simplicial_attention_b200 import shard
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
 
+    def seq_forward(leaves):
+        return shard.sequence_parallel_attn(leaves[0], (leaves[1], leaves[2]), (leaves[3], leaves[4]),
+                                            w1=w1, w2=w2, kernel=args.kernel)
+
     def step_resident():
+        if seq:
+            leaves = [t.detach().requires_grad_() for t in (q, k1, k2, v1, v2)]
+            out = seq_forward(leaves)
+            out.backward(do)
+            return out, [t.grad for t in leaves]
         out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=args.kernel)
         return out, sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=args.kernel)
 
@@ -226,9 +244,15 @@ def main():
         for s in range(steps):
             flush.zero_()
             ev[s][0].record()
-            out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=args.kernel)
-            ev[s][1].record()
-            sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=args.kernel)
+            if seq:
+                leaves = [t.detach().requires_grad_() for t in (q, k1, k2, v1, v2)]
+                out = seq_forward(leaves)          # includes the halo exchange
+                ev[s][1].record()
+                out.backward(do)                   # includes the exchange of the halo gradients
+            else:
+                out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=args.kernel)
+                ev[s][1].record()
+                sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=args.kernel)
             ev[s][2].record()
         torch.cuda.synchronize()
         fwd = [e[0].elapsed_time(e[1]) for e in ev]
@@ -243,8 +267,8 @@ def main():
     def step_e2e():
         ins = [t.to(dev, non_blocking=True) for t in host]
         leaves = [t.requires_grad_() for t in ins[:5]]
-        out = sa.sliding_two_simplicial_attn(leaves[0], (leaves[1], leaves[2]), (leaves[3], leaves[4]),
-                                             w1=w1, w2=w2, causal=True, kernel=args.kernel)
+        out = seq_forward(leaves) if seq else sa.sliding_two_simplicial_attn(
+            leaves[0], (leaves[1], leaves[2]), (leaves[3], leaves[4]), w1=w1, w2=w2, causal=True, kernel=args.kernel)
         out.backward(ins[5])
         out_h.copy_(out.detach(), non_blocking=True)
         for h_, l_ in zip(dq_h, leaves):
@@ -305,7 +329,9 @@ def main():
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, **cfg, "global_batch": cfg["b"] * world, "kernel": args.kernel,
-                   "sharding": "batch x head per rank, no collective", "l2": "256 MB buffer written between timed steps"},
+                   "sharding": ("sequence blocks, NCCL send/recv of the w1-1 / w2-1 row halo" if seq
+                                else "batch x head per rank, no collective"),
+                   "l2": "256 MB buffer written between timed steps"},
         "tokens_per_s": cfg["b"] * cfg["n"] * world / (ms_per_step * 1e-3),
         "e2e": None if args.no_e2e else {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms / args.steps},

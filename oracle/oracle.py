@@ -60,6 +60,9 @@ def _forward_chunked(q, k1, k2, v1, v2, w1, w2, scale, chunk):
     assert hq % hk == 0
     g = hq // hk
     dv = v1.shape[-1]
+    # keys may carry extra leading rows (the halo of the previous sequence block):
+    # query row i then sits at key row i + off
+    off1, off2 = k1.shape[1] - n, k2.shape[1] - n
 
     # (b, hk, g, n, d) queries; (b, hk, n, d) keys / values
     qh = q.permute(0, 2, 1, 3).reshape(b, hk, g, n, d) * scale
@@ -68,17 +71,17 @@ def _forward_chunked(q, k1, k2, v1, v2, w1, w2, scale, chunk):
     outs, lses = [], []
     for i0 in range(0, n, chunk):
         i1 = min(n, i0 + chunk)
-        j0 = max(0, i0 - w1 + 1)
-        m0 = max(0, i0 - w2 + 1)
+        j0 = max(0, i0 + off1 - w1 + 1)
+        m0 = max(0, i0 + off2 - w2 + 1)
         qi = qh[:, :, :, i0:i1]
-        kj, vj = k1h[:, :, j0:i1], v1h[:, :, j0:i1]
-        km, vm = k2h[:, :, m0:i1], v2h[:, :, m0:i1]
+        kj, vj = k1h[:, :, j0:i1 + off1], v1h[:, :, j0:i1 + off1]
+        km, vm = k2h[:, :, m0:i1 + off2], v2h[:, :, m0:i1 + off2]
 
         sim = torch.einsum("bhgid,bhjd,bhkd->bhgijk", qi, kj, km)
 
         ii = torch.arange(i0, i1)[:, None]
-        dj = ii - torch.arange(j0, i1)[None, :]
-        dk = ii - torch.arange(m0, i1)[None, :]
+        dj = ii + off1 - torch.arange(j0, i1 + off1)[None, :]
+        dk = ii + off2 - torch.arange(m0, i1 + off2)[None, :]
         ok = ((dj >= 0) & (dj < w1))[:, :, None] & ((dk >= 0) & (dk < w2))[:, None, :]
         sim = sim.masked_fill(~ok, float("-inf"))
 
@@ -179,6 +182,13 @@ def lse_row0(q, k1, k2, scale=None):
     k1e = k1[:, 0].repeat_interleave(g, dim=1)
     k2e = k2[:, 0].repeat_interleave(g, dim=1)
     return scale * (q[:, 0] * k1e * k2e).sum(-1)
+
+
+def attend(q, keys, values, w1=512, w2=32, causal=True, **_):
+    """Differentiable CPU stand-in with the signature of ``sliding_two_simplicial_attn``."""
+    assert causal
+    out, _ = _forward_chunked(q, keys[0], keys[1], values[0], values[1], w1, w2, q.shape[-1] ** -0.5, 32)
+    return out
 
 
 __all__ = [
