@@ -33,8 +33,24 @@ def shard_batch_heads(t: Tensor, rank: int, world: int, dim: int = 0) -> Tensor:
     return t.narrow(dim, rank * step, step)
 
 
+def _via_host(send, recv, group, fn) -> bool:
+    """gloo moves host memory only: stage device tensors through the host (tests on one GPU)."""
+    tensors = (send or []) + (recv or [])
+    if dist.get_backend(group) != "gloo" or not any(t.is_cuda for t in tensors):
+        return False
+    send_h = [t.cpu() for t in send] if send is not None else None
+    recv_h = [torch.empty(t.shape, dtype=t.dtype) for t in recv] if recv is not None else None
+    fn(send_h, recv_h, group)
+    if recv is not None:
+        for d, h in zip(recv, recv_h):
+            d.copy_(h)
+    return True
+
+
 def _exchange(send_right: list[Tensor] | None, recv_left: list[Tensor] | None, group) -> None:
     """One step of the chain: post every send to rank+1 and every recv from rank-1, then wait."""
+    if _via_host(send_right, recv_left, group, _exchange):
+        return
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     ops = []
     if recv_left is not None and rank > 0:
@@ -50,6 +66,8 @@ def _exchange(send_right: list[Tensor] | None, recv_left: list[Tensor] | None, g
 
 def _exchange_back(send_left: list[Tensor] | None, recv_right: list[Tensor] | None, group) -> None:
     """The mirror step: sends go to rank-1, receives come from rank+1."""
+    if _via_host(send_left, recv_right, group, _exchange_back):
+        return
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     ops = []
     if recv_right is not None and rank < world - 1:
