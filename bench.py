@@ -179,12 +179,84 @@ def run_reference(args, cfg, name):
     print(json.dumps(line), flush=True)
 
 
+C4 = dict(dim=512, depth=8, heads=8, key_value_heads=4, dim_head=64, every=2, vocab=256, batch=16, seq_len=1024,
+          w1=512, w2=32)
+
+
+def run_c4(args):
+    """Full training step of the 8-layer decoder (every 2nd layer simplicial, byte vocabulary,
+    batch 16 x 1024 tokens per GPU, bf16 autocast, Adam): tokens/s.  N > 1: data parallel (DDP)."""
+    from simplicial_attention_b200.transformer import TwoSimplicialLM, training_step
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(0)
+    c = C4
+    model = TwoSimplicialLM(num_tokens=c["vocab"], dim=c["dim"], depth=c["depth"], max_seq_len=c["seq_len"],
+                            dim_head=c["dim_head"], heads=c["heads"], two_simplicial_attn_every=c["every"],
+                            transformer_kwargs=dict(key_value_heads=c["key_value_heads"],
+                                                    two_simplicial_attn_kwargs=dict(w1=c["w1"], w2=c["w2"], qk_rmsnorm=True))).to(dev)
+    net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    opt = torch.optim.Adam(net.parameters(), lr=1e-4)
+    gen = torch.Generator().manual_seed(100 + rank)
+    host = torch.randint(0, c["vocab"], (c["batch"], c["seq_len"] + 1), generator=gen, dtype=torch.uint8).pin_memory()
+    resident = host.to(dev).long()
+
+    def step(tokens):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            return training_step(net, opt, tokens)
+
+    for _ in range(max(3, args.warmup)):
+        step(resident)
+    sampler = ClockSampler(local)
+    barrier(world)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(resident)
+    e1.record()
+    barrier(world)
+    ms = reduce_max(e0.elapsed_time(e1), world) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    # end to end: token ids from pinned host memory every step, loss read back every step
+    barrier(world)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step(host.to(dev, non_blocking=True).long())
+        loss_host = loss.item()
+    e1.record()
+    barrier(world)
+    e2e_ms = reduce_max(e0.elapsed_time(e1), world) / args.steps
+    if rank == 0:
+        tokens = c["batch"] * c["seq_len"] * world
+        simplicial_layers = c["depth"] // c["every"]
+        print(json.dumps({
+            "metric": "training tokens/s (8-layer decoder, every 2nd layer 2-simplicial)", "value": tokens / (ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "C4", **c, "global_batch": c["batch"] * world, "parallelism": f"dp{world}",
+                       "optimizer": "Adam lr 1e-4, grad clip 0.5"},
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": host.numel(),
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms, "last_loss": loss_host},
+            "gpu_launches": args.steps * simplicial_layers * 5, "clocks": clocks}), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="C3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="C3", choices=sorted(WORKLOADS) + ["C4"])
     ap.add_argument("--kernel", default="auto", choices=("auto", "simt", "tcgen05"))
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--sharding", default="batch", choices=("batch", "seq"),
@@ -193,6 +265,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
     args = ap.parse_args()
+    if args.workload == "C4":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the decoder training step has no CPU reference arm; "
+                              "the operator's arm is --workload C3"}), flush=True)
+            return
+        run_c4(args)
+        return
     cfg = dict(WORKLOADS[args.workload])
 
     if args.impl == "reference":

@@ -177,6 +177,11 @@ def sliding_two_simplicial_attn(
     assert len(keys) == len(values) == 2
     k1, k2 = keys
     v1, v2 = values
+    if q.is_cuda and torch.is_autocast_enabled():
+        # under autocast the norms in front of the attention hand over fp32: run in the autocast dtype
+        dt = torch.get_autocast_dtype("cuda")
+        if dt in _DTYPES:
+            q, k1, k2, v1, v2 = (t.to(dt) for t in (q, k1, k2, v1, v2))
     return SlidingTwoSimplicialAttention.apply(q, k1, k2, v1, v2, w1, w2, causal, None, kernel, return_lse)
 
 

@@ -42,11 +42,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // Bounded wait.  `abort_flag` is a CTA-wide shared word: once any thread gives
 // up, every later wait in the CTA returns false at once.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+// `sleep_ns` > 0 makes the poller yield its issue slots between tries (used by
+// whole warps that wait; the single MMA-issuing lanes poll without sleeping).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned sleep_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     int spins = 0;
     while (!mbar_try_wait(bar, parity)) {
+        if (sleep_ns) __nanosleep(sleep_ns);
         if ((++spins & 255) == 0) {
             if (*abort_flag) return false;
             if (clock64() - t0 > WAIT_LIMIT_CYCLES) {

@@ -1,0 +1,45 @@
+"""Decoder stack / LM wrapper (the training-step harness)."""
+import pytest
+import torch
+
+from simplicial_attention_b200.transformer import TwoSimplicialLM, TwoSimplicialTransformer, training_step
+
+
+def _lm(**kw):
+    return TwoSimplicialLM(num_tokens=256, dim=128, depth=4, max_seq_len=64, dim_head=32, heads=4,
+                           two_simplicial_attn_every=2,
+                           transformer_kwargs=dict(key_value_heads=2, two_simplicial_attn_kwargs=dict(w1=16, w2=4)), **kw)
+
+
+def test_parameter_names_follow_the_reference():
+    keys = set(_lm().state_dict())
+    # standard layer 0, simplicial layer 1 (every 2nd), feed-forward, embeddings, head
+    for k in ("token_emb.weight", "pos_emb.weight", "to_logits.weight", "transformer.norm.weight",
+              "transformer.layers.0.0.prenorm.weight", "transformer.layers.0.0.to_q.weight",
+              "transformer.layers.0.0.to_kv.weight", "transformer.layers.0.0.to_out.weight",
+              "transformer.layers.0.1.0.weight", "transformer.layers.0.1.1.weight", "transformer.layers.0.1.3.bias",
+              "transformer.layers.1.0.prenorm.weight", "transformer.layers.1.0.to_qkv.weight",
+              "transformer.layers.1.0.q_norm.weight", "transformer.layers.1.0.k_norms.1.weight",
+              "transformer.layers.1.0.v_norms.0.weight", "transformer.layers.1.0.combine_heads.weight"):
+        assert k in keys, k
+    assert "transformer.layers.0.0.to_qkv.weight" not in keys and "transformer.layers.1.0.to_kv.weight" not in keys
+
+
+def test_layer_pattern():
+    t = TwoSimplicialTransformer(64, depth=8, heads=2, key_value_heads=2, dim_head=32, two_simplicial_attn_every=2)
+    kinds = [type(a).__name__ for a, _ in t.layers]
+    assert kinds == ["Attention", "SlidingWindowTwoSimplicialMHA"] * 4
+
+
+@pytest.mark.gpu
+def test_training_steps_reduce_the_loss():
+    torch.manual_seed(0)
+    model = _lm().cuda()
+    opt = torch.optim.Adam(model.parameters(), lr=3e-3)
+    tokens = torch.randint(0, 256, (4, 65), device="cuda")
+    losses = []
+    for _ in range(12):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            losses.append(training_step(model, opt, tokens).item())
+    assert all(l == l for l in losses)                  # finite
+    assert losses[-1] < losses[0] - 0.3, losses         # memorises the fixed batch
