@@ -244,37 +244,49 @@ __device__ __forceinline__ int bq_compute_body(const BqParams &P, const BqGeom &
             tmem_ld32(lane_addr + 320 + wb * 128 + hf * 32, w);
             tmem_wait_ld();
             if (ok) {
+                // three passes (k2 -> dQ, q -> dK2, dO -> dV2); in each the four 16-byte loads are issued
+                // together, so a pass costs one memory latency instead of four
                 const __nv_bfloat16 *kr = k2 + elem_off(kp.k2, b, kk, hk) + hf * 32;
+                uint4 raw[4];
+#pragma unroll
+                for (int v8 = 0; v8 < 4; ++v8) raw[v8] = __ldg(reinterpret_cast<const uint4 *>(kr + v8 * 8));
 #pragma unroll
                 for (int v8 = 0; v8 < 4; ++v8) {
-                    const uint4 kraw = *reinterpret_cast<const uint4 *>(kr + v8 * 8);
-                    const uint4 qraw = *reinterpret_cast<const uint4 *>(qrow + hf * 32 + v8 * 8);
-                    const uint4 draw = *reinterpret_cast<const uint4 *>(dorow + hf * 32 + v8 * 8);
-                    const uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
-                    const uint32_t qw[4] = {qraw.x, qraw.y, qraw.z, qraw.w};
-                    const uint32_t dw[4] = {draw.x, draw.y, draw.z, draw.w};
-                    float xk[8], xv[8];
+                    const uint32_t kw[4] = {raw[v8].x, raw[v8].y, raw[v8].z, raw[v8].w};
 #pragma unroll
                     for (int z = 0; z < 4; ++z) {
                         const __nv_bfloat162 k2v = *reinterpret_cast<const __nv_bfloat162 *>(&kw[z]);
-                        const __nv_bfloat162 q2v = *reinterpret_cast<const __nv_bfloat162 *>(&qw[z]);
-                        const __nv_bfloat162 d2v = *reinterpret_cast<const __nv_bfloat162 *>(&dw[z]);
                         const int x = v8 * 8 + z * 2;
-                        const float u0 = __uint_as_float(u[x]), u1 = __uint_as_float(u[x + 1]);
-                        const float w0 = __uint_as_float(w[x]), w1 = __uint_as_float(w[x + 1]);
-                        dq[hf * 32 + x] = fmaf(u0, __low2float(k2v), dq[hf * 32 + x]);
-                        dq[hf * 32 + x + 1] = fmaf(u1, __high2float(k2v), dq[hf * 32 + x + 1]);
-                        xk[z * 2] = u0 * __low2float(q2v); xk[z * 2 + 1] = u1 * __high2float(q2v);
-                        xv[z * 2] = w0 * __low2float(d2v); xv[z * 2 + 1] = w1 * __high2float(d2v);
+                        dq[hf * 32 + x] = fmaf(__uint_as_float(u[x]), __low2float(k2v), dq[hf * 32 + x]);
+                        dq[hf * 32 + x + 1] = fmaf(__uint_as_float(u[x + 1]), __high2float(k2v), dq[hf * 32 + x + 1]);
                     }
+                }
 #pragma unroll
-                    for (int f4 = 0; f4 < 2; ++f4) {
-                        float4 *pk = reinterpret_cast<float4 *>(ak + hf * 32 + v8 * 8 + f4 * 4);
-                        float4 *pv = reinterpret_cast<float4 *>(av + hf * 32 + v8 * 8 + f4 * 4);
-                        float4 tk = *pk, tv = *pv;
-                        tk.x += xk[f4 * 4]; tk.y += xk[f4 * 4 + 1]; tk.z += xk[f4 * 4 + 2]; tk.w += xk[f4 * 4 + 3];
-                        tv.x += xv[f4 * 4]; tv.y += xv[f4 * 4 + 1]; tv.z += xv[f4 * 4 + 2]; tv.w += xv[f4 * 4 + 3];
-                        *pk = tk; *pv = tv;
+                for (int pass = 0; pass < 2; ++pass) {
+                    const __nv_bfloat16 *mrow = (pass == 0 ? qrow : dorow) + hf * 32;
+                    float *arow = (pass == 0 ? ak : av) + hf * 32;
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; ++v8) raw[v8] = __ldg(reinterpret_cast<const uint4 *>(mrow + v8 * 8));
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; ++v8) {
+                        const uint32_t mw[4] = {raw[v8].x, raw[v8].y, raw[v8].z, raw[v8].w};
+                        float x8[8];
+#pragma unroll
+                        for (int z = 0; z < 4; ++z) {
+                            const __nv_bfloat162 m2 = *reinterpret_cast<const __nv_bfloat162 *>(&mw[z]);
+                            const int x = v8 * 8 + z * 2;
+                            const float t0 = __uint_as_float(pass == 0 ? u[x] : w[x]);
+                            const float t1 = __uint_as_float(pass == 0 ? u[x + 1] : w[x + 1]);
+                            x8[z * 2] = t0 * __low2float(m2);
+                            x8[z * 2 + 1] = t1 * __high2float(m2);
+                        }
+#pragma unroll
+                        for (int f4 = 0; f4 < 2; ++f4) {
+                            float4 *pa = reinterpret_cast<float4 *>(arow + v8 * 8 + f4 * 4);
+                            float4 tv = *pa;
+                            tv.x += x8[f4 * 4]; tv.y += x8[f4 * 4 + 1]; tv.z += x8[f4 * 4 + 2]; tv.w += x8[f4 * 4 + 3];
+                            *pa = tv;
+                        }
                     }
                 }
             }
