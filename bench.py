@@ -49,8 +49,8 @@ WORKLOADS = {
     "C3": dict(b=4, hq=8, hk=8, n=4096, d=64, w1=512, w2=32),
     "C5": dict(b=8, hq=16, hk=16, n=16384, d=128, w1=512, w2=32),
 }
-# CPU sample: one batch element, two heads, up to 4096 rows of the same head dim and windows
-CPU_SAMPLE = dict(b=1, hq=2, hk=2, n=4096)
+# CPU sample: two batch elements, eight heads, up to 4096 rows of the same head dim and windows (~10 s on 16 cores)
+CPU_SAMPLE = dict(b=2, hq=8, hk=8, n=4096)
 
 
 def valid_pairs(n, w1, w2):
@@ -403,6 +403,10 @@ def main():
     bwd_tf = fl["bwd"] / (bwd_avg * 1e-3) / 1e12
     min_bytes = {"fwd": 6 * cfg["b"] * cfg["n"] * cfg["hq"] * cfg["d"] * 2, "bwd": 12 * cfg["b"] * cfg["n"] * cfg["hq"] * cfg["d"] * 2}
 
+    # DRAM bytes per launch from the ncu captures summarised under profiles/ (C3, tensor-core kernels):
+    # backward = dK1/dV1 kernel 115.6 MB + dQ/dK2/dV2 kernel 293.4 MB; forward 91.4 MB
+    traffic_bwd = 409.0e6 if (args.workload == "C3" and args.kernel == "auto" and not seq) else None
+    traffic_fwd = 91.4e6 if (args.workload == "C3" and args.kernel == "auto" and not seq) else None
     line = {
         "metric": "2-simplicial attn fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
@@ -416,10 +420,10 @@ def main():
                 "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": launches * args.steps,
         "roofline": {"bound": "tensor", "kernel": "sa2_bwd", "achieved": bwd_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": bwd_tf / peaks["tflops"], "traffic": None, "peak_source": peaks["source"],
+                     "frac": bwd_tf / peaks["tflops"], "traffic": traffic_bwd, "peak_source": peaks["source"],
                      "ms_per_launch": bwd_avg},
         "roofline_fwd": {"bound": "tensor", "kernel": "sa2_fwd", "achieved": fwd_tf, "peak": peaks["tflops"],
-                         "unit": "TFLOP/s", "frac": fwd_tf / peaks["tflops"], "ms_per_launch": fwd_avg},
+                         "unit": "TFLOP/s", "frac": fwd_tf / peaks["tflops"], "traffic": traffic_fwd, "ms_per_launch": fwd_avg},
         "hbm_min_gbs": {"fwd": min_bytes["fwd"] / (fwd_avg * 1e-3) / 1e9, "bwd": min_bytes["bwd"] / (bwd_avg * 1e-3) / 1e9,
                         "peak": peaks["hbm_gbs"]},
         "clocks": clocks,
