@@ -21,8 +21,8 @@
 // Row i-e of the shared accumulators is touched by exactly one thread per
 // sweep, so the read-modify-write needs no atomics.
 //
-// Warps (320 threads): 0 TMA producer, 1 MMA issuer + TMEM owner, 2-5 compute,
-// 6-9 builders.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
+// Warps (448 threads): 0 TMA producer, 1 MMA issuer + TMEM owner, 2-5 compute (P, G),
+// 6-9 fold (U, W into dQ / dK2 / dV2, concurrently with the next sweep's compute), 10-13 builders.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
 // 128h+128); sweep parity p -> U [256+128p, +64), W [320+128p, +64).
 #pragma once
 #include "sa2_tc_bwd_k1.cuh"
@@ -30,7 +30,7 @@
 namespace sa2 {
 namespace tc {
 
-constexpr int BQ_THREADS = 320;
+constexpr int BQ_THREADS = 448;
 constexpr int BQ_MAX_TILES = 3;          // K1/V1 tiles resident per CTA
 constexpr int BQ_ACC_STRIDE = 68;        // floats per accumulator row (64 + 4: conflict-free row-per-thread access)
 constexpr int BQ_MAX_W2 = 56;            // the shared accumulators hold 127 + w2 rows; beyond this they do not fit
@@ -92,11 +92,11 @@ __device__ __forceinline__ BqGeom bq_geom(const BqParams &P) {
     return g;
 }
 
-// ---------------------------------------------------------------- builders (warps 6-9)
+// ---------------------------------------------------------------- builders (warps 10-13)
 __device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, uint8_t *sA, uint8_t *sB,
                                           uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
-    const int r = threadIdx.x - 192;
+    const int r = threadIdx.x - 320;
     const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
     const int i = g.i0 + r;
     const bool iv = i < kp.n;
@@ -194,37 +194,79 @@ __device__ __forceinline__ int bq_mma(const BqGeom &g, uint32_t tmem, uint8_t *s
     return 0;
 }
 
-// ---------------------------------------------------------------- compute (warps 2-5)
-__device__ __forceinline__ void bq_compute_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-__device__ __forceinline__ int bq_compute_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
-                                               uint64_t *bars, volatile int *abort_flag) {
+// ---------------------------------------------------------------- compute (warps 2-5): P and G
+__device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, uint32_t tmem, uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ct = threadIdx.x - 64;                  // 0..127 among the compute threads
     const int r = (warp & 3) * 32 + lane;             // query row within the tile = TMEM lane
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
-    const int split = blockIdx.x % P.nsplit;
+    const int h = blockIdx.y, b = blockIdx.z;
     const int i = g.i0 + r;
     const bool row_ok = i < kp.n;
     const float c = P.c;
-    const int acc_rows = 127 + kp.w2;
-
-    // zero the shared accumulators
-    for (int x = ct; x < 2 * acc_rows * BQ_ACC_STRIDE; x += 128) acc_k[x] = 0.f;    // acc_v follows acc_k
-    bq_compute_sync();
-
     float lse2 = 0.f, dl = 0.f;
     if (row_ok) {
         const int64_t o = ((int64_t)b * kp.hq + h) * kp.n + i;
         lse2 = kp.lse[o] * 1.4426950408889634f;
         dl = kp.delta[o];
     }
+    for (int e = 0; e < g.nsweeps; ++e) {
+        const bool sweep_ok = row_ok && (i + kp.off2 - e >= 0);
+        for (int within = 0; within < g.upe; ++within) {
+            const int u = e * g.upe + within, jt = within >> 1, half = within & 1;
+            const int j0 = g.jbase + TJ * (g.t_begin + jt) + 64 * half;
+            const int d1 = i + kp.off1 - j0;
+            const int hi = sweep_ok ? min(d1, 63) : -1;         // valid columns: lo < col <= hi
+            const int lo = max(d1 - kp.w1, -j0 - 1);
+            if (!warp_wait(&bars[BQ_S_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_COMPUTE;
+            tc_fence_after();
+            const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+                uint32_t sv[32], dv[32], pp[16], gg[16];
+                tmem_ld32(lane_addr + half * 128 + ch * 32, sv);
+                tmem_ld32(lane_addr + half * 128 + 64 + ch * 32, dv);
+                tmem_wait_ld();
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                    float p0 = ex2(fmaf(__uint_as_float(sv[x]), c, -lse2));
+                    float p1 = ex2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
+                    if (!full) {
+                        const int col = ch * 32 + x;
+                        p0 = (col > lo && col <= hi) ? p0 : 0.f;
+                        p1 = (col + 1 > lo && col + 1 <= hi) ? p1 : 0.f;
+                    }
+                    pp[x >> 1] = pack_bf16(p0, p1);
+                    gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
+                }
+                // P / G chunk over columns of S / dP that have already been read
+                tmem_st16(lane_addr + half * 128 + ch * 16, pp);
+                tmem_st16(lane_addr + half * 128 + 64 + ch * 16, gg);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars[BQ_P_FULL + half]);
+        }
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------- fold (warps 6-9): U, W -> dQ, dK2, dV2
+__device__ __forceinline__ void bq_fold_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
+                                            uint64_t *bars, volatile int *abort_flag) {
+    const KernelParams &kp = P.kp;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = (warp & 3) * 32 + lane;             // query row within the tile = TMEM lane
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
+    const int split = blockIdx.x % P.nsplit;
+    const int i = g.i0 + r;
+    const bool row_ok = i < kp.n;
     float dq[64];
 #pragma unroll
     for (int x = 0; x < 64; ++x) dq[x] = 0.f;
-
     const __nv_bfloat16 *qrow = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, row_ok ? i : 0, h);
     const __nv_bfloat16 *dorow = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, row_ok ? i : 0, h);
     const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
@@ -296,46 +338,13 @@ __device__ __forceinline__ int bq_compute_body(const BqParams &P, const BqGeom &
         return true;
     };
 
-    for (int e = 0; e < g.nsweeps; ++e) {
-        const bool sweep_ok = row_ok && (i + kp.off2 - e >= 0);
-        for (int within = 0; within < g.upe; ++within) {
-            const int u = e * g.upe + within, jt = within >> 1, half = within & 1;
-            const int j0 = g.jbase + TJ * (g.t_begin + jt) + 64 * half;
-            const int d1 = i + kp.off1 - j0;
-            const int hi = sweep_ok ? min(d1, 63) : -1;         // valid columns: lo < col <= hi
-            const int lo = max(d1 - kp.w1, -j0 - 1);
-            if (!warp_wait(&bars[BQ_S_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_COMPUTE;
-            tc_fence_after();
-            const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
-            uint32_t pp[32], gg[32];
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t sv[32], dv[32];
-                tmem_ld32(lane_addr + half * 128 + ch * 32, sv);
-                tmem_ld32(lane_addr + half * 128 + 64 + ch * 32, dv);
-                tmem_wait_ld();
-#pragma unroll
-                for (int x = 0; x < 32; x += 2) {
-                    float p0 = ex2(fmaf(__uint_as_float(sv[x]), c, -lse2));
-                    float p1 = ex2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
-                    if (!full) {
-                        const int col = ch * 32 + x;
-                        p0 = (col > lo && col <= hi) ? p0 : 0.f;
-                        p1 = (col + 1 > lo && col + 1 <= hi) ? p1 : 0.f;
-                    }
-                    pp[ch * 16 + (x >> 1)] = pack_bf16(p0, p1);
-                    gg[ch * 16 + (x >> 1)] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
-                }
-            }
-            tmem_st32(lane_addr + half * 128, pp);
-            tmem_st32(lane_addr + half * 128 + 64, gg);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&bars[BQ_P_FULL + half]);
-            if (within == 0 && e >= 1 && !drain(e - 1)) return ERR_BQ_COMPUTE;
+    if (g.total > 0)
+        for (int e = 0; e < g.nsweeps; ++e) {
+            if (!drain(e)) return ERR_BQ_COMPUTE;
+            // Row i-e of the shared accumulators is written by thread r in this sweep and by thread r+1 in
+            // the next: every fold thread must have finished sweep e (all have arrived on W_EMPTY) first.
+            if (!warp_wait(&bars[BQ_W_EMPTY + (e & 1)], (e >> 1) & 1, abort_flag)) return ERR_BQ_COMPUTE;
         }
-    }
-    if (g.total > 0 && !drain(g.nsweeps - 1)) return ERR_BQ_COMPUTE;
 
     // partial dQ of this split
     if (row_ok) {
@@ -347,20 +356,23 @@ __device__ __forceinline__ int bq_compute_body(const BqParams &P, const BqGeom &
     return 0;
 }
 
-__device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
-                                          uint64_t *bars, volatile int *abort_flag) {
+__device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
+                                       uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
-    const int ct = threadIdx.x - 64;
+    const int ft = threadIdx.x - 192;                 // 0..127 among the fold threads
     const int h = blockIdx.y, b = blockIdx.z;
     const int qt = blockIdx.x / P.nsplit, split = blockIdx.x % P.nsplit;
     const int acc_rows = 127 + kp.w2;
-    const int err = bq_compute_body(P, g, tmem, acc_k, acc_v, bars, abort_flag);
+    // zero the shared accumulators (acc_v follows acc_k); only this group touches them
+    for (int x = ft; x < 2 * acc_rows * BQ_ACC_STRIDE; x += 128) acc_k[x] = 0.f;
+    bq_fold_sync();
+    const int err = bq_fold_body(P, g, tmem, acc_k, acc_v, bars, abort_flag);
     // shared accumulators -> this CTA's slab.  The barrier sits outside the body so that a warp
     // that gave up on a wait still reaches it.
-    bq_compute_sync();
+    bq_fold_sync();
     float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + qt) * P.nsplit + split) * (size_t)(2 * acc_rows * 64);
-    for (int x = ct; x < 2 * acc_rows * 16; x += 128) {
-        const int row = x >> 4, c4 = (x & 15) * 4;      // row over both arrays (acc_v follows acc_k)
+    for (int x = ft; x < 2 * acc_rows * 16; x += 128) {
+        const int row = x >> 4, c4 = (x & 15) * 4;      // row over both arrays
         const float4 v = *reinterpret_cast<const float4 *>(acc_k + (size_t)row * BQ_ACC_STRIDE + c4);
         *reinterpret_cast<float4 *>(slab + (size_t)row * 64 + c4) = v;
     }
@@ -420,7 +432,9 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
         if (lane == 0 && g.total > 0) err = bq_mma(g, tmem, sK, sV, sA, sB, bars, abort_flag);
         __syncwarp();
     } else if (warp < 6) {
-        err = bq_compute(P, g, tmem, acc_k, acc_v, bars, abort_flag);
+        err = bq_compute(P, g, tmem, bars, abort_flag);
+    } else if (warp < 10) {
+        err = bq_fold(P, g, tmem, acc_k, acc_v, bars, abort_flag);
     } else if (g.total > 0) {
         err = bq_builder(P, g, sA, sB, bars, abort_flag);
     }
