@@ -21,7 +21,7 @@
 // Row i-e of the shared accumulators is touched by exactly one thread per
 // sweep, so the read-modify-write needs no atomics.
 //
-// Warps (448 threads): 0 TMA producer, 1 MMA issuer + TMEM owner, 2-5 compute (P, G),
+// Warps (448 threads): 0 TMA producer, then issuer of U / W; 1 TMEM owner and issuer of S / dP; 2-5 compute (P, G),
 // 6-9 fold (U, W into dQ / dK2 / dV2, concurrently with the next sweep's compute), 10-13 builders.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
 // 128h+128); sweep parity p -> U [256+128p, +64), W [320+128p, +64).
 #pragma once
@@ -43,7 +43,8 @@ enum BqBar {
     BQ_P_FULL = 5,       // [2]
     BQ_W_FULL = 7,       // [2]
     BQ_W_EMPTY = 9,      // [2]
-    BQ_BAR_COUNT = 11
+    BQ_G_DONE = 11,      // [2] per half: the U / W products of the unit have completed
+    BQ_BAR_COUNT = 13
 };
 
 enum { ERR_BQ_PRODUCER = 256, ERR_BQ_MMA = 512, ERR_BQ_COMPUTE = 1024, ERR_BQ_BUILDER = 2048 };
@@ -147,49 +148,71 @@ __device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, ui
     return 0;
 }
 
-// ---------------------------------------------------------------- MMA issuer (warp 1, one lane)
-__device__ __forceinline__ int bq_mma(const BqGeom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sA, uint8_t *sB,
-                                      uint64_t *bars, volatile int *abort_flag) {
+// ---------------------------------------------------------------- issuer of S, dP (warp 1, one lane)
+// Unit u = e * upe + within covers keys [64 (within & 1), +64) of tile within >> 1 of the split; units
+// alternate between the two halves, so half == u & 1.  One thread issues about one tcgen05.mma per 90
+// cycles, so the two product stages have an issuing thread each; U / W are accumulated by one thread
+// only, which keeps the summation order fixed.
+__device__ __forceinline__ int bq_mma_first(const BqGeom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sA, uint8_t *sB,
+                                            uint64_t *bars, volatile int *abort_flag) {
     constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);
-    constexpr uint32_t IDESC_G = idesc_bf16(128, 64, false, true);
-    const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aA = smem_u32(sA), aB = smem_u32(sB);
-
-    auto first = [&](int u) -> bool {
-        const int e = u / g.upe, within = u % g.upe, jt = within >> 1, half = within & 1;
-        if (within == 0 && !mbar_wait(&bars[BQ_AB_FULL], e & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t kt = aK + jt * TILE_BYTES + half * 8192, vt = aV + jt * TILE_BYTES + half * 8192;
-        const uint32_t d = tmem + half * 128;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(d, smem_desc_sw128(aA + 32 * k), smem_desc_sw128(kt + 32 * k), IDESC_F, k > 0);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(d + 64, smem_desc_sw128(aB + 32 * k), smem_desc_sw128(vt + 32 * k), IDESC_F, k > 0);
-        tc_commit(&bars[BQ_S_FULL + half]);
-        if (within == g.upe - 1) tc_commit(&bars[BQ_AB_EMPTY]);
-        return true;
-    };
-    auto second = [&](int u) -> bool {
-        const int e = u / g.upe, within = u % g.upe, jt = within >> 1, half = within & 1, wb = e & 1;
-        if (!mbar_wait(&bars[BQ_P_FULL + half], (u >> 1) & 1, abort_flag)) return false;
-        if (within == 0 && e >= 2 && !mbar_wait(&bars[BQ_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t kt = aK + jt * TILE_BYTES + half * 8192, vt = aV + jt * TILE_BYTES + half * 8192;
-        const uint32_t a = tmem + half * 128;
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-            mma_ts(tmem + 256 + wb * 128, a + 64 + 8 * k, smem_desc_sw128(kt + 2048 * k), IDESC_G, (within > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-            mma_ts(tmem + 320 + wb * 128, a + 8 * k, smem_desc_sw128(vt + 2048 * k), IDESC_G, (within > 0 || k > 0) ? 1u : 0u);
-        if (within == g.upe - 1) tc_commit(&bars[BQ_W_FULL + wb]);
-        return true;
-    };
-
+    const uint64_t dK = smem_desc_sw128(smem_u32(sK)), dV = smem_desc_sw128(smem_u32(sV));
+    const uint64_t dA = smem_desc_sw128(smem_u32(sA)), dB = smem_desc_sw128(smem_u32(sB));
     if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_MMA;
-    if (!first(0) || !first(1)) return ERR_BQ_MMA;
-    for (int u = 0; u < g.total; ++u) {
-        if (!second(u)) return ERR_BQ_MMA;
-        if (u + 2 < g.total && !first(u + 2)) return ERR_BQ_MMA;
+    int u = 0;
+    for (int e = 0; e < g.nsweeps; ++e) {
+        if (!mbar_wait(&bars[BQ_AB_FULL], e & 1, abort_flag)) return ERR_BQ_MMA;
+        for (int within = 0; within < g.upe; ++within, ++u) {
+            const int half = within & 1;
+            // the buffer holds P / G of this half's previous unit until its U / W products are done
+            if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
+            tc_fence_after();
+            const uint64_t off = (uint64_t)(((within >> 1) * TILE_BYTES + half * 8192) >> 4);
+            const uint64_t kt = dK + off, vt = dV + off;
+            const uint32_t d = tmem + half * 128;
+            mma_ss(d, dA, kt, IDESC_F, 0u);
+            mma_ss(d, dA + 2, kt + 2, IDESC_F, 1u);
+            mma_ss(d, dA + 4, kt + 4, IDESC_F, 1u);
+            mma_ss(d, dA + 6, kt + 6, IDESC_F, 1u);
+            mma_ss(d + 64, dB, vt, IDESC_F, 0u);
+            mma_ss(d + 64, dB + 2, vt + 2, IDESC_F, 1u);
+            mma_ss(d + 64, dB + 4, vt + 4, IDESC_F, 1u);
+            mma_ss(d + 64, dB + 6, vt + 6, IDESC_F, 1u);
+            tc_commit(&bars[BQ_S_FULL + half]);
+        }
+        tc_commit(&bars[BQ_AB_EMPTY]);
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------- issuer of U, W (warp 0, one lane)
+__device__ __forceinline__ int bq_mma_second(const BqGeom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV,
+                                             uint64_t *bars, volatile int *abort_flag) {
+    constexpr uint32_t IDESC_G = idesc_bf16(128, 64, false, true);
+    const uint64_t dK = smem_desc_sw128(smem_u32(sK)), dV = smem_desc_sw128(smem_u32(sV));
+    int u = 0;
+    for (int e = 0; e < g.nsweeps; ++e) {
+        const int wb = e & 1;
+        for (int within = 0; within < g.upe; ++within, ++u) {
+            const int half = within & 1;
+            if (!mbar_wait(&bars[BQ_P_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_MMA;
+            if (within == 0 && e >= 2 && !mbar_wait(&bars[BQ_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
+            tc_fence_after();
+            const uint64_t off = (uint64_t)(((within >> 1) * TILE_BYTES + half * 8192) >> 4);
+            const uint64_t kt = dK + off, vt = dV + off;
+            const uint32_t a = tmem + half * 128;
+            const uint32_t acc = within > 0 ? 1u : 0u;
+            mma_ts(tmem + 256 + wb * 128, a + 64, kt, IDESC_G, acc);           // U += G K1
+            mma_ts(tmem + 256 + wb * 128, a + 72, kt + 128, IDESC_G, 1u);
+            mma_ts(tmem + 256 + wb * 128, a + 80, kt + 256, IDESC_G, 1u);
+            mma_ts(tmem + 256 + wb * 128, a + 88, kt + 384, IDESC_G, 1u);
+            mma_ts(tmem + 320 + wb * 128, a, vt, IDESC_G, acc);                // W += P V1
+            mma_ts(tmem + 320 + wb * 128, a + 8, vt + 128, IDESC_G, 1u);
+            mma_ts(tmem + 320 + wb * 128, a + 16, vt + 256, IDESC_G, 1u);
+            mma_ts(tmem + 320 + wb * 128, a + 24, vt + 384, IDESC_G, 1u);
+            tc_commit(&bars[BQ_G_DONE + half]);
+        }
+        tc_commit(&bars[BQ_W_FULL + wb]);
     }
     return 0;
 }
@@ -426,10 +449,11 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
                 tma_load_4d(sV + (size_t)t * TILE_BYTES, &mapV, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
             }
             if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) err = ERR_BQ_PRODUCER;
+            else err = bq_mma_second(g, tmem, sK, sV, bars, abort_flag);
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0 && g.total > 0) err = bq_mma(g, tmem, sK, sV, sA, sB, bars, abort_flag);
+        if (lane == 0 && g.total > 0) err = bq_mma_first(g, tmem, sK, sV, sA, sB, bars, abort_flag);
         __syncwarp();
     } else if (warp < 6) {
         err = bq_compute(P, g, tmem, bars, abort_flag);
