@@ -16,6 +16,11 @@
 // The same shared-memory tile is the K-major B operand of the first product
 // and the MN-major B operand of the second.
 //
+// The per-query statistics are folded into the tensor-core products: every query row carries
+// -lse2_i / c and -D_i, each split into three bf16 terms, in a small extra tile, and a constant tile
+// of ones on the key side adds them with one more K=16 MMA, so that the accumulators already hold
+// S^T - lse2 / c and dP^T - D and the compute threads need no per-column loads.
+//
 // Warps (448 threads): 0 TMA producer, then issuer of the second products (dV1, dK1);
 // 1 TMEM owner and issuer of the first products (S^T, dP^T); 2-5 compute group of
 // half 0; 6-9 compute group of half 1; 10-13 builders.  One thread issues about one
@@ -53,7 +58,7 @@ struct BwdParams {
 };
 
 // padded above half of the SM's shared memory: one CTA per SM, so the 512-column TMEM allocation never waits
-inline size_t bk1_smem_bytes() { return 120 * 1024; }
+inline size_t bk1_smem_bytes() { return 1024 + 2 * TILE_BYTES + 4 * TILE_BYTES + 4 * TILE_BYTES + TILE_BYTES + 256; }
 
 struct Bk1Geom {
     int j0, i_lo, i_hi, n_it, total;
@@ -77,7 +82,19 @@ __device__ __forceinline__ Bk1Geom bk1_geom(const KernelParams &kp) {
 }
 
 // ---------------------------------------------------------------- builders (warps 10-13)
-__device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g, uint8_t *sAB, float *stats,
+// three bf16 terms whose sum is x to fp32 accuracy, packed with five zeros into one 16-byte chunk
+__device__ __forceinline__ uint4 split3_bf16(float x) {
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(x);
+    const float r1 = x - __bfloat162float(h0);
+    const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 h2 = __float2bfloat16_rn(r1 - __bfloat162float(h1));
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    v.x = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+    v.y = (uint32_t)__bfloat16_as_ushort(h2);
+    return v;
+}
+
+__device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g, uint8_t *sAB, uint8_t *sStat, uint8_t *sOnes,
                                            uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int r = threadIdx.x - 320;       // row of the query tile
@@ -86,6 +103,14 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
     const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
     const __nv_bfloat16 *dout = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p);
     const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p);
+    // the constant key-side tile: three ones per row (one per term of the split statistics)
+    {
+        uint4 one = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc)
+            *reinterpret_cast<uint4 *>(sOnes + sw128_offset(r, cc)) = cc == 0 ? one : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const float inv_c = 1.f / P.c;
     int s = 0, tile_counter = 0;
     for (int hh = 0; hh < kp.g; ++hh) {
         const int h = hk * kp.g + hh;
@@ -115,10 +140,13 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
                 if (s >= 2 && !warp_wait(&bars[BK1_AB_EMPTY + stage], ((s >> 1) - 1) & 1, abort_flag)) return ERR_BK1_BUILDER;
                 SA2_TRACE_MARK(r == 0 && s < 200, s * 4 + 1);
                 if (e == 0) {
-                    // column statistics of this query tile; the buffer of two tiles ago is no longer read
-                    float *st = stats + (tile_counter & 1) * 256;
-                    st[r] = lse2;
-                    st[128 + r] = dl;
+                    // statistics of this query tile (first 16 channels of two extra tiles); the buffer of
+                    // two tiles ago is no longer read
+                    uint8_t *stL = sStat + (size_t)(tile_counter & 1) * 2 * TILE_BYTES, *stD = stL + TILE_BYTES;
+                    *reinterpret_cast<uint4 *>(stL + sw128_offset(r, 0)) = split3_bf16(-lse2 * inv_c);
+                    *reinterpret_cast<uint4 *>(stL + sw128_offset(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4 *>(stD + sw128_offset(r, 0)) = split3_bf16(-dl);
+                    *reinterpret_cast<uint4 *>(stD + sw128_offset(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 uint8_t *dA = sAB + (size_t)stage * 2 * TILE_BYTES;
                 uint8_t *dB = dA + TILE_BYTES;
@@ -150,34 +178,42 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
 }
 
 // ---------------------------------------------------------------- issuer of S^T, dP^T (warp 1, one lane)
-__device__ __forceinline__ int bk1_mma_first(const Bk1Geom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sAB,
-                                             uint64_t *bars, volatile int *abort_flag) {
+__device__ __forceinline__ int bk1_mma_first(const KernelParams &kp, const Bk1Geom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV,
+                                             uint8_t *sAB, uint8_t *sStat, uint8_t *sOnes, uint64_t *bars, volatile int *abort_flag) {
     constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);
     const uint64_t dK = smem_desc_sw128(smem_u32(sK)), dV = smem_desc_sw128(smem_u32(sV));
     const uint64_t dAB = smem_desc_sw128(smem_u32(sAB));
+    const uint64_t dSt = smem_desc_sw128(smem_u32(sStat)), dOnes = smem_desc_sw128(smem_u32(sOnes));
     if (!mbar_wait(&bars[BK1_KV_FULL], 0, abort_flag)) return ERR_BK1_MMA;
-    for (int s = 0; s < g.total; ++s) {
-        const int stage = s & 1;
-        if (!mbar_wait(&bars[BK1_AB_FULL + stage], (s >> 1) & 1, abort_flag)) return ERR_BK1_MMA;
+    int s = 0, tile_counter = 0;
+    for (int hh = 0; hh < kp.g; ++hh) {
+        for (int t = 0; t < g.n_it; ++t, ++tile_counter) {
+            const int ne = bk1_sweeps(kp, g, t);
+            const uint64_t stL0 = dSt + (uint64_t)(((tile_counter & 1) * 2 * TILE_BYTES) >> 4);
+            for (int e = 0; e < ne; ++e, ++s) {
+                const int stage = s & 1;
+                if (!mbar_wait(&bars[BK1_AB_FULL + stage], (s >> 1) & 1, abort_flag)) return ERR_BK1_MMA;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            // the compute group must have read the previous step's S^T / dP^T of this half
-            SA2_TRACE_MARK(s < 200, 1000 + (s * 2 + half) * 4);
-            if (s >= 1 && !mbar_wait(&bars[BK1_P_FULL + half], (s - 1) & 1, abort_flag)) return ERR_BK1_MMA;
-            SA2_TRACE_MARK(s < 200, 1000 + (s * 2 + half) * 4 + 1);
-            tc_fence_after();
-            const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4), bq = a + (TILE_BYTES >> 4);
-            const uint32_t d = tmem + half * 128;
-            mma_ss(d, dK, a, IDESC_F, 0u);
-            mma_ss(d, dK + 2, a + 2, IDESC_F, 1u);
-            mma_ss(d, dK + 4, a + 4, IDESC_F, 1u);
-            mma_ss(d, dK + 6, a + 6, IDESC_F, 1u);
-            mma_ss(d + 64, dV, bq, IDESC_F, 0u);
-            mma_ss(d + 64, dV + 2, bq + 2, IDESC_F, 1u);
-            mma_ss(d + 64, dV + 4, bq + 4, IDESC_F, 1u);
-            mma_ss(d + 64, dV + 6, bq + 6, IDESC_F, 1u);
-            tc_commit(&bars[BK1_S_FULL + half]);
-            SA2_TRACE_MARK(s < 200, 1000 + (s * 2 + half) * 4 + 2);
+                for (int half = 0; half < 2; ++half) {
+                    // the compute group must have read the previous step's S^T / dP^T of this half
+                    if (s >= 1 && !mbar_wait(&bars[BK1_P_FULL + half], (s - 1) & 1, abort_flag)) return ERR_BK1_MMA;
+                    tc_fence_after();
+                    const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4), bq = a + (TILE_BYTES >> 4);
+                    const uint64_t stL = stL0 + (uint64_t)((half * 8192) >> 4), stD = stL + (TILE_BYTES >> 4);
+                    const uint32_t d = tmem + half * 128;
+                    mma_ss(d, dK, a, IDESC_F, 0u);
+                    mma_ss(d, dK + 2, a + 2, IDESC_F, 1u);
+                    mma_ss(d, dK + 4, a + 4, IDESC_F, 1u);
+                    mma_ss(d, dK + 6, a + 6, IDESC_F, 1u);
+                    mma_ss(d, dOnes, stL, IDESC_F, 1u);               // - lse2_i / c
+                    mma_ss(d + 64, dV, bq, IDESC_F, 0u);
+                    mma_ss(d + 64, dV + 2, bq + 2, IDESC_F, 1u);
+                    mma_ss(d + 64, dV + 4, bq + 4, IDESC_F, 1u);
+                    mma_ss(d + 64, dV + 6, bq + 6, IDESC_F, 1u);
+                    mma_ss(d + 64, dOnes, stD, IDESC_F, 1u);          // - D_i
+                    tc_commit(&bars[BK1_S_FULL + half]);
+                }
+            }
         }
     }
     return 0;
@@ -216,7 +252,7 @@ __device__ __forceinline__ int bk1_mma_second(const Bk1Geom &g, uint32_t tmem, u
 }
 
 // ---------------------------------------------------------------- compute (group h = half h: warps 2-5, 6-9)
-__device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g, int half, uint32_t tmem, const float *stats,
+__device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g, int half, uint32_t tmem,
                                            uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -233,12 +269,9 @@ __device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g,
         for (int t = 0; t < g.n_it; ++t, ++tile_counter) {
             const int it0 = g.i_lo + TQ * t;
             const int ne = bk1_sweeps(kp, g, t);
-            const float *st = stats + (tile_counter & 1) * 256 + half * 64;
             const int base = j - kp.off1 - it0;                       // column of the diagonal i + off1 == j
             const int hi = (jv ? min(min(TQ - 1, base + kp.w1 - 1), g.i_hi - it0) : -1) - half * 64;
             for (int e = 0; e < ne; ++e, ++s) {
-                // the builders' statistics (written before they signalled this stage) must be visible
-                if (e == 0 && !warp_wait(&bars[BK1_AB_FULL + (s & 1)], (s >> 1) & 1, abort_flag)) return ERR_BK1_COMPUTE;
                 const int lo = max(max(0, base), e - kp.off2 - it0) - half * 64;     // valid columns: lo <= col <= hi
                 SA2_TRACE_MARK(r == 0 && s < 200, 5000 + (s * 2 + half) * 4);
                 if (!warp_wait(&bars[BK1_S_FULL + half], s & 1, abort_flag)) return ERR_BK1_COMPUTE;
@@ -253,38 +286,25 @@ __device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g,
                     tmem_ld32(buf + ch * 32, sv);
                     tmem_ld32(buf + 64 + ch * 32, dv);
                     tmem_wait_ld();
-                    const float4 *l4 = reinterpret_cast<const float4 *>(st + ch * 32);
-                    const float4 *d4 = reinterpret_cast<const float4 *>(st + 128 + ch * 32);
+                    // the accumulators already hold S^T - lse2 / c and dP^T - D
                     if (full) {
 #pragma unroll
-                        for (int x4 = 0; x4 < 8; ++x4) {
-                            const float4 lv = l4[x4], dl = d4[x4];
-                            const float p0 = ex2(fmaf(__uint_as_float(sv[x4 * 4]), c, -lv.x));
-                            const float p1 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 1]), c, -lv.y));
-                            const float p2 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 2]), c, -lv.z));
-                            const float p3 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 3]), c, -lv.w));
-                            pk[x4 * 2] = pack_bf16(p0, p1);
-                            pk[x4 * 2 + 1] = pack_bf16(p2, p3);
-                            gk[x4 * 2] = pack_bf16(p0 * (__uint_as_float(dv[x4 * 4]) - dl.x), p1 * (__uint_as_float(dv[x4 * 4 + 1]) - dl.y));
-                            gk[x4 * 2 + 1] = pack_bf16(p2 * (__uint_as_float(dv[x4 * 4 + 2]) - dl.z), p3 * (__uint_as_float(dv[x4 * 4 + 3]) - dl.w));
+                        for (int x = 0; x < 32; x += 2) {
+                            const float p0 = ex2(__uint_as_float(sv[x]) * c);
+                            const float p1 = ex2(__uint_as_float(sv[x + 1]) * c);
+                            pk[x >> 1] = pack_bf16(p0, p1);
+                            gk[x >> 1] = pack_bf16(p0 * __uint_as_float(dv[x]), p1 * __uint_as_float(dv[x + 1]));
                         }
                     } else {
 #pragma unroll
-                        for (int x4 = 0; x4 < 8; ++x4) {
-                            const float4 lv = l4[x4], dl = d4[x4];
-                            const int col = ch * 32 + x4 * 4;
-                            float p0 = ex2(fmaf(__uint_as_float(sv[x4 * 4]), c, -lv.x));
-                            float p1 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 1]), c, -lv.y));
-                            float p2 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 2]), c, -lv.z));
-                            float p3 = ex2(fmaf(__uint_as_float(sv[x4 * 4 + 3]), c, -lv.w));
+                        for (int x = 0; x < 32; x += 2) {
+                            const int col = ch * 32 + x;
+                            float p0 = ex2(__uint_as_float(sv[x]) * c);
+                            float p1 = ex2(__uint_as_float(sv[x + 1]) * c);
                             p0 = (col >= lo && col <= hi) ? p0 : 0.f;
                             p1 = (col + 1 >= lo && col + 1 <= hi) ? p1 : 0.f;
-                            p2 = (col + 2 >= lo && col + 2 <= hi) ? p2 : 0.f;
-                            p3 = (col + 3 >= lo && col + 3 <= hi) ? p3 : 0.f;
-                            pk[x4 * 2] = pack_bf16(p0, p1);
-                            pk[x4 * 2 + 1] = pack_bf16(p2, p3);
-                            gk[x4 * 2] = pack_bf16(p0 * (__uint_as_float(dv[x4 * 4]) - dl.x), p1 * (__uint_as_float(dv[x4 * 4 + 1]) - dl.y));
-                            gk[x4 * 2 + 1] = pack_bf16(p2 * (__uint_as_float(dv[x4 * 4 + 2]) - dl.z), p3 * (__uint_as_float(dv[x4 * 4 + 3]) - dl.w));
+                            pk[x >> 1] = pack_bf16(p0, p1);
+                            gk[x >> 1] = pack_bf16(p0 * __uint_as_float(dv[x]), p1 * __uint_as_float(dv[x + 1]));
                         }
                     }
                     tmem_st16(pg + ch * 16, pk);
@@ -329,8 +349,9 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     uint8_t *sK = smem;
     uint8_t *sV = sK + TILE_BYTES;
     uint8_t *sAB = sV + TILE_BYTES;                       // 2 stages x (A tile, B tile)
-    float *stats = reinterpret_cast<float *>(sAB + 4 * TILE_BYTES);   // 2 buffers x (lse2[128], D[128])
-    uint64_t *bars = reinterpret_cast<uint64_t *>(stats + 512);
+    uint8_t *sStat = sAB + 4 * TILE_BYTES;                // 2 buffers x (-lse2/c tile, -D tile), 16 channels used
+    uint8_t *sOnes = sStat + 4 * TILE_BYTES;              // constant: three ones per row
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sOnes + TILE_BYTES);
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + BK1_BAR_COUNT);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
 
@@ -371,12 +392,12 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0 && g.total > 0) err = bk1_mma_first(g, tmem, sK, sV, sAB, bars, abort_flag);
+        if (lane == 0 && g.total > 0) err = bk1_mma_first(P.kp, g, tmem, sK, sV, sAB, sStat, sOnes, bars, abort_flag);
         __syncwarp();
     } else if (warp < 10) {
-        err = bk1_compute(P, g, (warp - 2) >> 2, tmem, stats, bars, abort_flag);
+        err = bk1_compute(P, g, (warp - 2) >> 2, tmem, bars, abort_flag);
     } else {
-        err = bk1_builder(P, g, sAB, stats, bars, abort_flag);
+        err = bk1_builder(P, g, sAB, sStat, sOnes, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
 
