@@ -107,7 +107,11 @@ inline int bwd(const KernelParams &kp, const sa2_shape &s, void *extra, cudaStre
         return SA2_ERR_CUDA;
     if (cudaFuncSetAttribute(bwd_k1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bk1_smem_bytes()) != cudaSuccess)
         return SA2_ERR_CUDA;
-    bwd_k1_kernel<<<dim3((kp.nk1 + TJ - 1) / TJ, kp.hk, kp.b), BK1_THREADS, bk1_smem_bytes(), st>>>(mapK, mapV, P);
+    CUtensorMap mapK2, mapV2;      // second keys / values, 32-row boxes
+    if (!tmap::make_rows_map(&mapK2, kp.k2.p, kp.b, kp.nk2, kp.hk, 64, kp.k2.sb, kp.k2.sn, kp.k2.sh, 32) ||
+        !tmap::make_rows_map(&mapV2, kp.v2.p, kp.b, kp.nk2, kp.hk, 64, kp.v2.sb, kp.v2.sn, kp.v2.sh, 32))
+        return SA2_ERR_CUDA;
+    bwd_k1_kernel<<<dim3((kp.nk1 + TJ - 1) / TJ, kp.hk, kp.b), BK1_THREADS, bk1_smem_bytes(), st>>>(mapK, mapV, mapK2, mapV2, P);
     if (cudaGetLastError() != cudaSuccess) return SA2_ERR_CUDA;
 
     if (bq_supported(s)) {

@@ -46,7 +46,9 @@ enum Bk1Bar {
     BK1_P_FULL = 7,      // [2] per half
     BK1_G_DONE = 9,      // [2] per half: second products of the step have completed
     BK1_DONE = 11,
-    BK1_BAR_COUNT = 12
+    BK1_WIN_FREE = 12,   // the builders have finished reading the k2/v2 window of the previous query tile
+    BK1_WIN_FULL = 13,   // the window of the current query tile has landed
+    BK1_BAR_COUNT = 14
 };
 
 enum { ERR_BK1_PRODUCER = 16, ERR_BK1_MMA = 32, ERR_BK1_COMPUTE = 64, ERR_BK1_BUILDER = 128 };
@@ -58,7 +60,10 @@ struct BwdParams {
 };
 
 // padded above half of the SM's shared memory: one CTA per SM, so the 512-column TMEM allocation never waits
-inline size_t bk1_smem_bytes() { return 1024 + 2 * TILE_BYTES + 4 * TILE_BYTES + 4 * TILE_BYTES + TILE_BYTES + 256; }
+constexpr int BK1_WIN_ROWS = 160;    // second-key / second-value rows a query tile can pair with: 32 + 128
+inline size_t bk1_smem_bytes() {
+    return 1024 + 2 * TILE_BYTES + 4 * TILE_BYTES + 4 * TILE_BYTES + TILE_BYTES + 2 * BK1_WIN_ROWS * 128 + 256;
+}
 
 struct Bk1Geom {
     int j0, i_lo, i_hi, n_it, total;
@@ -94,7 +99,8 @@ __device__ __forceinline__ uint4 split3_bf16(float x) {
     return v;
 }
 
-__device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g, uint8_t *sAB, uint8_t *sStat, uint8_t *sOnes,
+__device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g, const CUtensorMap *mapK2, const CUtensorMap *mapV2,
+                                           uint8_t *sAB, uint8_t *sStat, uint8_t *sOnes, uint8_t *sWin,
                                            uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int r = threadIdx.x - 320;       // row of the query tile
@@ -118,6 +124,22 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
             const int i = g.i_lo + TQ * t + r;
             const bool iv = i <= g.i_hi;
             const int ne = bk1_sweeps(kp, g, t);
+            // The k2 / v2 rows this query tile pairs with over all sweeps (positions it0 - 32 .. it0 + 127)
+            // are staged once per tile by TMA; every step then reads its rows from shared memory.
+            const bool win = kp.w2 <= 32;
+            if (win) {
+                if (tile_counter > 0) mbar_arrive(&bars[BK1_WIN_FREE]);
+                if (r == 0) {
+                    if (tile_counter > 0 && !mbar_wait(&bars[BK1_WIN_FREE], (tile_counter - 1) & 1, abort_flag)) return ERR_BK1_BUILDER;
+                    mbar_arrive_expect_tx(&bars[BK1_WIN_FULL], 2 * BK1_WIN_ROWS * 128);
+                    const int row0 = g.i_lo + TQ * t + kp.off2 - 32;
+                    for (int bx = 0; bx < BK1_WIN_ROWS / 32; ++bx) {
+                        tma_load_4d(sWin + bx * 4096, mapK2, &bars[BK1_WIN_FULL], 0, hk, row0 + 32 * bx, b);
+                        tma_load_4d(sWin + BK1_WIN_ROWS * 128 + bx * 4096, mapV2, &bars[BK1_WIN_FULL], 0, hk, row0 + 32 * bx, b);
+                    }
+                }
+                if (!mbar_wait(&bars[BK1_WIN_FULL], tile_counter & 1, abort_flag, 64)) return ERR_BK1_BUILDER;
+            }
             uint4 qv[8], dv[8];
 #pragma unroll
             for (int cc = 0; cc < 8; ++cc) { qv[cc] = make_uint4(0, 0, 0, 0); dv[cc] = make_uint4(0, 0, 0, 0); }
@@ -154,12 +176,16 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
                 const bool ok = iv && kk >= 0;
                 const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
                 const __nv_bfloat16 *vp2 = v2 + elem_off(kp.v2, b, ok ? kk : 0, hk);
+                const int wr = r + 32 - e;                       // row of the staged window
+                const uint8_t *wk = sWin + wr * 128, *wv = wk + BK1_WIN_ROWS * 128;
 #pragma unroll
                 for (int cc = 0; cc < 8; ++cc) {
                     uint4 a = make_uint4(0, 0, 0, 0), bb = make_uint4(0, 0, 0, 0);
                     if (ok) {
-                        const uint4 kv = *reinterpret_cast<const uint4 *>(kp2 + cc * 8);
-                        const uint4 vv = *reinterpret_cast<const uint4 *>(vp2 + cc * 8);
+                        const uint4 kv = win ? *reinterpret_cast<const uint4 *>(wk + ((cc ^ (wr & 7)) << 4))
+                                             : *reinterpret_cast<const uint4 *>(kp2 + cc * 8);
+                        const uint4 vv = win ? *reinterpret_cast<const uint4 *>(wv + ((cc ^ (wr & 7)) << 4))
+                                             : *reinterpret_cast<const uint4 *>(vp2 + cc * 8);
                         a.x = mul_bf16x2(qv[cc].x, kv.x); a.y = mul_bf16x2(qv[cc].y, kv.y);
                         a.z = mul_bf16x2(qv[cc].z, kv.z); a.w = mul_bf16x2(qv[cc].w, kv.w);
                         bb.x = mul_bf16x2(dv[cc].x, vv.x); bb.y = mul_bf16x2(dv[cc].y, vv.y);
@@ -343,7 +369,8 @@ __device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g,
 }
 
 __global__ void __launch_bounds__(BK1_THREADS, 1)
-bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, const BwdParams P) {
+bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+              const __grid_constant__ CUtensorMap mapK2, const __grid_constant__ CUtensorMap mapV2, const BwdParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sK = smem;
@@ -351,14 +378,16 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     uint8_t *sAB = sV + TILE_BYTES;                       // 2 stages x (A tile, B tile)
     uint8_t *sStat = sAB + 4 * TILE_BYTES;                // 2 buffers x (-lse2/c tile, -D tile), 16 channels used
     uint8_t *sOnes = sStat + 4 * TILE_BYTES;              // constant: three ones per row
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sOnes + TILE_BYTES);
+    uint8_t *sWin = sOnes + TILE_BYTES;                   // staged k2 rows, then v2 rows (160 x 128 B each)
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sWin + 2 * BK1_WIN_ROWS * 128);
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + BK1_BAR_COUNT);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int x = 0; x < BK1_BAR_COUNT; ++x) {
-            const bool many = (x >= BK1_AB_FULL && x < BK1_AB_FULL + 2) || (x >= BK1_P_FULL && x < BK1_P_FULL + 2);
+            const bool many = (x >= BK1_AB_FULL && x < BK1_AB_FULL + 2) || (x >= BK1_P_FULL && x < BK1_P_FULL + 2) ||
+                              x == BK1_WIN_FREE;
             mbar_init(&bars[x], many ? 128u : 1u);
         }
         *abort_flag = 0;
@@ -397,7 +426,7 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     } else if (warp < 10) {
         err = bk1_compute(P, g, (warp - 2) >> 2, tmem, bars, abort_flag);
     } else {
-        err = bk1_builder(P, g, sAB, sStat, sOnes, bars, abort_flag);
+        err = bk1_builder(P, g, &mapK2, &mapV2, sAB, sStat, sOnes, sWin, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
 
