@@ -291,9 +291,9 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
         for (int cc = 0; cc < 8; ++cc) {
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
             if (ok) {
-                const uint4 a = *reinterpret_cast<const uint4 *>(qrow + cc * 8);
+                const uint4 a = __ldg(reinterpret_cast<const uint4 *>(qrow + cc * 8));
                 const uint4 kv = k2_in_smem ? *reinterpret_cast<const uint4 *>(sK2 + sw128_offset(r + 32 - e, cc))
-                                            : *reinterpret_cast<const uint4 *>(krow + cc * 8);
+                                            : __ldg(reinterpret_cast<const uint4 *>(krow + cc * 8));
                 v.x = mul_bf16x2(a.x, kv.x); v.y = mul_bf16x2(a.y, kv.y);
                 v.z = mul_bf16x2(a.z, kv.z); v.w = mul_bf16x2(a.w, kv.w);
             }
@@ -321,7 +321,7 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
                 const __nv_bfloat16 *vp = v2 + elem_off(kp.v2, b, kk, hk) + half * 32;
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    const uint4 raw = *reinterpret_cast<const uint4 *>(vp + u * 8);
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(vp + u * 8));
                     const uint32_t rr[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
                     for (int z = 0; z < 4; ++z) {
