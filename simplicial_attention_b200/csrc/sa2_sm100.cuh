@@ -151,6 +151,10 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+// Per-warpgroup register budget (all four warps of an aligned warpgroup must execute it).
+template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor for tiles stored as rows of 128 bytes with the
 // 128-byte swizzle (16-byte chunk index XOR (row & 7)); 8 rows form a 1024-byte

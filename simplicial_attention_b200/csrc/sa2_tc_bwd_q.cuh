@@ -21,8 +21,10 @@
 // Row i-e of the shared accumulators is touched by exactly one thread per
 // sweep, so the read-modify-write needs no atomics.
 //
-// Warps (448 threads): 0 TMA producer, then issuer of U / W; 1 TMEM owner and issuer of S / dP; 2-5 compute (P, G),
-// 6-9 fold (U, W into dQ / dK2 / dV2, concurrently with the next sweep's compute), 10-13 builders.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
+// Warps (512 threads, four aligned warpgroups): 0 TMA producer, then issuer of U / W; 1 TMEM owner and
+// issuer of S / dP; 2, 3 idle; 4-7 compute (P, G); 8-11 fold (U, W into dQ / dK2 / dV2, concurrently with
+// the next sweep's compute); 12-15 builders.  Every thread starts with 128 registers; the issuer
+// warpgroup releases all but 24 (setmaxnreg) and the fold and builder groups take them over.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
 // 128h+128); sweep parity p -> U [256+128p, +64), W [320+128p, +64).
 #pragma once
 #include "sa2_tc_bwd_k1.cuh"
@@ -30,7 +32,12 @@
 namespace sa2 {
 namespace tc {
 
-constexpr int BQ_THREADS = 448;
+constexpr int BQ_THREADS = 512;
+// Register hand-over between warpgroups.  Four warps per scheduler partition start with 128 registers a
+// thread; a group can only grow by what another has released, or its setmaxnreg never returns, so the
+// four budgets must add up to 4 * 128.
+constexpr int BQ_REGS_LAUNCH = 128, BQ_REGS_ISSUE = 40, BQ_REGS_COMPUTE = 120, BQ_REGS_FOLD = 192, BQ_REGS_BUILD = 160;
+static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BQ_REGS_FOLD + BQ_REGS_BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
 constexpr int BQ_MAX_TILES = 3;          // K1/V1 tiles resident per CTA
 constexpr int BQ_ACC_STRIDE = 68;        // floats per accumulator row (64 + 4: conflict-free row-per-thread access)
 constexpr int BQ_MAX_W2 = 56;            // the shared accumulators hold 127 + w2 rows; beyond this they do not fit
@@ -93,11 +100,11 @@ __device__ __forceinline__ BqGeom bq_geom(const BqParams &P) {
     return g;
 }
 
-// ---------------------------------------------------------------- builders (warps 10-13)
+// ---------------------------------------------------------------- builders (warps 12-15)
 __device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, uint8_t *sA, uint8_t *sB,
                                           uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
-    const int r = threadIdx.x - 320;
+    const int r = threadIdx.x - 384;
     const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
     const int i = g.i0 + r;
     const bool iv = i < kp.n;
@@ -217,7 +224,7 @@ __device__ __forceinline__ int bq_mma_second(const BqGeom &g, uint32_t tmem, uin
     return 0;
 }
 
-// ---------------------------------------------------------------- compute (warps 2-5): P and G
+// ---------------------------------------------------------------- compute (warps 4-7): P and G
 __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, uint32_t tmem, uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -274,7 +281,7 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
     return 0;
 }
 
-// ---------------------------------------------------------------- fold (warps 6-9): U, W -> dQ, dK2, dV2
+// ---------------------------------------------------------------- fold (warps 8-11): U, W -> dQ, dK2, dV2
 __device__ __forceinline__ void bq_fold_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
@@ -382,7 +389,7 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 __device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
                                        uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
-    const int ft = threadIdx.x - 192;                 // 0..127 among the fold threads
+    const int ft = threadIdx.x - 256;                 // 0..127 among the fold threads
     const int h = blockIdx.y, b = blockIdx.z;
     const int qt = blockIdx.x / P.nsplit, split = blockIdx.x % P.nsplit;
     const int acc_rows = 127 + kp.w2;
@@ -437,30 +444,36 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     const BqGeom g = bq_geom(P);
 
     int err = 0;
-    if (warp == 0) {
-        if (lane == 0 && g.total > 0) {
-            const int hk = blockIdx.y / P.kp.g;
-            prefetch_tmap(&mapK);
-            prefetch_tmap(&mapV);
-            mbar_arrive_expect_tx(&bars[BQ_KV_FULL], 2 * TILE_BYTES * g.ntl);
-            for (int t = 0; t < g.ntl; ++t) {
-                const int row = g.jbase + TJ * (g.t_begin + t);
-                tma_load_4d(sK + (size_t)t * TILE_BYTES, &mapK, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
-                tma_load_4d(sV + (size_t)t * TILE_BYTES, &mapV, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+    if (warp < 4) {
+        reg_dealloc<BQ_REGS_ISSUE>();                 // one instruction for the whole warpgroup
+        if (warp == 0) {
+            if (lane == 0 && g.total > 0) {
+                const int hk = blockIdx.y / P.kp.g;
+                prefetch_tmap(&mapK);
+                prefetch_tmap(&mapV);
+                mbar_arrive_expect_tx(&bars[BQ_KV_FULL], 2 * TILE_BYTES * g.ntl);
+                for (int t = 0; t < g.ntl; ++t) {
+                    const int row = g.jbase + TJ * (g.t_begin + t);
+                    tma_load_4d(sK + (size_t)t * TILE_BYTES, &mapK, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+                    tma_load_4d(sV + (size_t)t * TILE_BYTES, &mapV, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+                }
+                if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) err = ERR_BQ_PRODUCER;
+                else err = bq_mma_second(g, tmem, sK, sV, bars, abort_flag);
             }
-            if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) err = ERR_BQ_PRODUCER;
-            else err = bq_mma_second(g, tmem, sK, sV, bars, abort_flag);
+            __syncwarp();
+        } else if (warp == 1) {
+            if (lane == 0 && g.total > 0) err = bq_mma_first(g, tmem, sK, sV, sA, sB, bars, abort_flag);
+            __syncwarp();
         }
-        __syncwarp();
-    } else if (warp == 1) {
-        if (lane == 0 && g.total > 0) err = bq_mma_first(g, tmem, sK, sV, sA, sB, bars, abort_flag);
-        __syncwarp();
-    } else if (warp < 6) {
+    } else if (warp < 8) {
+        reg_dealloc<BQ_REGS_COMPUTE>();
         err = bq_compute(P, g, tmem, bars, abort_flag);
-    } else if (warp < 10) {
+    } else if (warp < 12) {
+        reg_alloc<BQ_REGS_FOLD>();
         err = bq_fold(P, g, tmem, acc_k, acc_v, bars, abort_flag);
-    } else if (g.total > 0) {
-        err = bq_builder(P, g, sA, sB, bars, abort_flag);
+    } else {
+        reg_alloc<BQ_REGS_BUILD>();
+        if (g.total > 0) err = bq_builder(P, g, sA, sB, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
 
