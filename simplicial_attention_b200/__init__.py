@@ -13,6 +13,7 @@ from .attention import (
     sliding_two_simplicial_attn,
     sliding_two_simplicial_attn_with_lse,
 )
+from .host import HostPipeline
 from .mha import HigherOrderAttention, SlidingWindowTwoSimplicialMHA
 
 __all__ = [
@@ -22,6 +23,7 @@ __all__ = [
     "sa2_forward",
     "sa2_backward",
     "device_status",
+    "HostPipeline",
     "HigherOrderAttention",
     "SlidingWindowTwoSimplicialMHA",
 ]

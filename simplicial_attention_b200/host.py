@@ -1,0 +1,85 @@
+"""Forward + backward of the sliding-window 2-simplicial attention for tensors that live in HOST memory.
+
+The reference's operator takes CUDA tensors only
+(simplicial_attention/triton_two_simplicial_attention.py:729); a caller whose
+activations sit in pinned host memory pays a host->device copy before and a
+device->host copy after every call.  Batch elements are independent, so
+``HostPipeline`` cuts a call into batch chunks and runs three streams: chunk
+``c+1`` is copied in while chunk ``c`` is computed and chunk ``c-1`` is copied
+out.  Calls may be queued back to back (the host tensors must already hold their
+data when ``run`` is called); ``synchronize()`` waits for all of them.
+PCIe is full duplex, so in steady state a call costs the larger of its compute
+time and one direction's copy time instead of their sum.
+
+Everything is computed by the CUDA library behind the C ABI (``sa2_fwd`` /
+``sa2_bwd``); this file only schedules copies and launches.
+"""
+from __future__ import annotations
+
+import torch
+
+from .attention import sa2_backward, sa2_forward
+
+
+class HostPipeline:
+    """``run(inputs, outputs)`` with ``inputs = (q, k1, k2, v1, v2, dout)`` and
+    ``outputs = (out, dq, dk1, dk2, dv1, dv2)``, all pinned host tensors of
+    layout ``(b, n, h, d)``; results are valid after ``synchronize()``."""
+
+    def __init__(self, device, w1=512, w2=32, chunk=2, slots=2, kernel="auto"):
+        self.device = torch.device(device)
+        self.w1, self.w2, self.chunk, self.kernel = int(w1), int(w2), int(chunk), kernel
+        self.s_in = torch.cuda.Stream(self.device)
+        self.s_run = torch.cuda.Stream(self.device)
+        self.s_out = torch.cuda.Stream(self.device)
+        self.slots = [None] * slots          # device copies of one chunk's six inputs
+        self.free = [None] * slots           # event: the slot's inputs are no longer read
+        self.turn = 0
+
+    def _stage(self, slot, parts):
+        bufs = self.slots[slot]
+        if bufs is None or any(b.shape != p.shape or b.dtype != p.dtype for b, p in zip(bufs, parts)):
+            bufs = [torch.empty(p.shape, dtype=p.dtype, device=self.device) for p in parts]
+            self.slots[slot] = bufs
+        return bufs
+
+    def run(self, inputs, outputs):
+        assert len(inputs) == 6 and len(outputs) == 6
+        assert all(t.is_pinned() for t in (*inputs, *outputs)), "host tensors must be pinned"
+        b = inputs[0].shape[0]
+        for b0 in range(0, b, self.chunk):
+            sl = slice(b0, min(b, b0 + self.chunk))
+            slot = self.turn % len(self.slots)
+            self.turn += 1
+            parts = [t[sl] for t in inputs]
+            with torch.cuda.stream(self.s_in):
+                if self.free[slot] is not None:
+                    self.s_in.wait_event(self.free[slot])
+                dev = self._stage(slot, parts)
+                for d_, p_ in zip(dev, parts):
+                    d_.copy_(p_, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(self.s_in)
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(ready)
+                q, k1, k2, v1, v2, dout = dev
+                out, lse = sa2_forward(q, k1, k2, v1, v2, self.w1, self.w2, kernel=self.kernel)
+                grads = sa2_backward(q, k1, k2, v1, v2, out, lse, dout, self.w1, self.w2, kernel=self.kernel)
+                done = torch.cuda.Event()
+                done.record(self.s_run)
+                self.free[slot] = done
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(done)
+                for h_, d_ in zip(outputs, (out, *grads)):
+                    h_[sl].copy_(d_, non_blocking=True)
+                    d_.record_stream(self.s_out)
+
+    def join(self):
+        """Make the caller's current stream wait for everything queued so far."""
+        end = torch.cuda.Event()
+        end.record(self.s_out)
+        torch.cuda.current_stream(self.device).wait_event(end)
+
+    def synchronize(self):
+        """Block the host until every queued call has delivered its results."""
+        self.s_out.synchronize()
