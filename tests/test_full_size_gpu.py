@@ -1,0 +1,100 @@
+"""Parity at the full benchmark sizes, through properties that do not need the oracle on the whole problem.
+
+C3 (b4 h8 n4096 d64 w1=512 w2=32, bf16, tensor-core kernels) and a C5-shaped case (n16384 d128, fp32
+kernels on bf16 tensors; two (batch, head) pairs of C5's 128):
+
+* crop against the oracle: rows [s, s+L) of one (batch, head) depend only on keys back to s-w1+1, and the
+  key-side gradients of rows [s, s+L-w1] only on queries inside the crop, so the oracle run on the crop
+  (with its halo) must reproduce those rows of the full-size result;
+* gradients are exactly linear in dO: doubling dO doubles every gradient bit for bit;
+* row 0 sees one (j, k) pair: out_0 = v1_0 * v2_0 and lse_0 = scale * sum(q_0 k1_0 k2_0);
+* v1 = v2 = 1 gives out = 1 and (near-)zero dq, dk1, dk2.
+"""
+import pytest
+import torch
+
+import simplicial_attention_b200 as sa
+from oracle import oracle as O
+from util import max_abs
+
+pytestmark = pytest.mark.gpu
+
+GRADS = ("dq", "dk1", "dk2", "dv1", "dv2")
+
+
+def run(ins, w1, w2):
+    q, k1, k2, v1, v2, do = ins
+    out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2)
+    grads = sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, grad_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert sa.device_status() == 0
+    res = {"out": out, "lse": lse}
+    res.update(dict(zip(GRADS, grads)))
+    return res
+
+
+def crop_check(res, ins, w1, w2, b, h, s, length, tol):
+    """Oracle on rows [s, s+length) of (batch b, head h) with their halo, against the full-size result."""
+    q, k1, k2, v1, v2, do = ins
+    e = s + length
+    o1, o2 = min(w1 - 1, s), min(w2 - 1, s)
+    hs = slice(h, h + 1)
+    crop = (q[b:b + 1, s:e, hs], k1[b:b + 1, s - o1:e, hs], k2[b:b + 1, s - o2:e, hs],
+            v1[b:b + 1, s - o1:e, hs], v2[b:b + 1, s - o2:e, hs], do[b:b + 1, s:e, hs])
+    ref = O.two_simplicial_fwd_bwd(*crop, w1, w2)
+    got = {k: v.float().cpu() for k, v in res.items()}
+    assert max_abs(got["out"][b:b + 1, s:e, hs], ref["out"]) <= tol
+    assert max_abs(got["lse"][b:b + 1, hs, s:e], ref["lse"]) <= tol
+    assert max_abs(got["dq"][b:b + 1, s:e, hs], ref["dq"]) <= tol
+    # key rows whose every contributing query lies inside the crop
+    m1, m2 = length - w1 + 1, length - w2 + 1
+    assert max_abs(got["dk1"][b:b + 1, s:s + m1, hs], ref["dk1"][:, o1:o1 + m1]) <= tol
+    assert max_abs(got["dv1"][b:b + 1, s:s + m1, hs], ref["dv1"][:, o1:o1 + m1]) <= tol
+    assert max_abs(got["dk2"][b:b + 1, s:s + m2, hs], ref["dk2"][:, o2:o2 + m2]) <= tol
+    assert max_abs(got["dv2"][b:b + 1, s:s + m2, hs], ref["dv2"][:, o2:o2 + m2]) <= tol
+
+
+def row0_check(res, ins, tol):
+    q, k1, k2, v1, v2, _ = (t.float() for t in ins)
+    d = q.shape[-1]
+    want = v1[:, 0] * v2[:, 0]
+    # one (j, k) pair with probability 1: the product itself, rounded to the output type (one bf16 ulp allowed)
+    assert ((res["out"][:, 0].float() - want).abs() <= want.abs() * 2.0 ** -7 + 1e-6).all()
+    lse0 = (q[:, 0] * k1[:, 0] * k2[:, 0]).sum(-1) * d ** -0.5
+    assert max_abs(res["lse"][:, :, 0], lse0) <= tol
+
+
+def test_c3_full_size_tensor_core_kernels():
+    b, n, h, d, w1, w2 = 4, 4096, 8, 64, 512, 32
+    ins = [t.cuda() for t in O.make_inputs(b, n, h, h, d, seed=33, dtype=torch.bfloat16)]
+    res = run(ins, w1, w2)
+    row0_check(res, ins, 1e-2)
+    crop_check(res, ins, w1, w2, b=1, h=3, s=0, length=640, tol=2e-2)        # sequence start: truncated windows
+    crop_check(res, ins, w1, w2, b=3, h=6, s=2500, length=1100, tol=2e-2)    # interior, unaligned to the 128-row tiles
+    # exact linearity in dO (scaling by two is exact in every product and rounding)
+    ins2 = ins[:5] + [ins[5] * 2]
+    res2 = run(ins2, w1, w2)
+    for k in GRADS:
+        assert torch.equal(res2[k], res[k] * 2), k
+    assert torch.equal(res2["out"], res["out"])
+
+
+def test_c3_full_size_unit_values():
+    b, n, h, d, w1, w2 = 4, 4096, 8, 64, 512, 32
+    q, k1, k2, v1, v2, do = (t.cuda() for t in O.make_inputs(b, n, h, h, d, seed=34, dtype=torch.bfloat16))
+    v1, v2 = torch.ones_like(v1), torch.ones_like(v2)
+    res = run([q, k1, k2, v1, v2, do], w1, w2)
+    assert max_abs(res["out"].float(), torch.ones_like(res["out"], dtype=torch.float32)) <= 1e-2
+    for k in ("dq", "dk1", "dk2"):
+        assert res[k].abs().max().item() <= 2e-2, k
+
+
+def test_c5_shape_fp32_kernels():
+    # C5's sequence length, head dimension and windows; 2 of its 128 (batch, head) pairs
+    b, n, h, d, w1, w2 = 1, 16384, 2, 128, 512, 32
+    ins = [t.cuda() for t in O.make_inputs(b, n, h, h, d, seed=35, dtype=torch.bfloat16)]
+    res = run(ins, w1, w2)
+    row0_check(res, ins, 1e-2)
+    # bf16 tensors, fp32 arithmetic: the only rounding is the stored bf16 output (also inside D = rowsum(O dO))
+    crop_check(res, ins, w1, w2, b=0, h=1, s=9000, length=700, tol=1.5e-2)
+    crop_check(res, ins, w1, w2, b=0, h=0, s=n - 600, length=600, tol=1.5e-2)   # sequence end
