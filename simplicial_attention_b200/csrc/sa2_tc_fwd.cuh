@@ -11,21 +11,24 @@
 // v2_{i-e} * W_e to its output registers.  The softmax is joint over all
 // (j, e): one denominator per row.
 //
-// Warp roles (320 threads):
-//   warp 0      TMA producer: the K1/V1 window and the 127 + 32 second-key rows
-//               the tile can pair with, loaded once and resident in shared memory;
-//               then issues the tcgen05.mma stream of group 1 (one lane)
-//   warp 1      owns the TMEM allocation, issues the tcgen05.mma stream of group 0
-//   warps 2-5   softmax group 0: even sweeps, one thread per query row
-//   warps 6-9   softmax group 1: odd sweeps, one thread per query row
-// A group builds the A tile of its next sweep itself (row r by the thread that
-// owns row r) as soon as the last S product of its current sweep has completed,
-// so the tile is ready long before the tensor cores need it.
+// Warp roles (512 threads, four aligned warpgroups):
+//   warp 0        TMA producer: the K1/V1 window and the 127 + 32 second-key rows
+//                 the tile can pair with, loaded once and resident in shared memory;
+//                 then issues the tcgen05.mma stream of group 1 (one lane)
+//   warp 1        owns the TMEM allocation, issues the tcgen05.mma stream of group 0
+//   warps 2-3     idle (they fill the issuers' warpgroup)
+//   warps 4-7     softmax group 0: even sweeps, one thread per query row
+//   warps 8-11    softmax group 1: odd sweeps, one thread per query row
+//   warps 12-15   output group, one thread per query row: builds the A tile of each
+//                 group's next sweep as soon as the last S product of its current sweep
+//                 has completed, and at the end of a sweep adds v2_{i-e} * W_e to the
+//                 row's output registers (one accumulator per softmax group)
 // An even and an odd sweep are in flight together, so while one group runs the
 // exponentials of its tile the tensor cores work for the other and each SM
-// sub-partition has two softmax warps to hide latencies.  Every
-// group keeps its own (reference, denominator, output) state per row; the two
-// states are merged through shared memory at the end.
+// sub-partition has two softmax warps to hide latencies.  A softmax thread keeps
+// only (reference, denominator) per row; the output thread keeps the two groups'
+// accumulators, each against the reference its group last reported, and merges
+// them at the end.  Registers move between the warpgroups with setmaxnreg.
 //
 // The unit of the pipeline is half a key tile (64 keys): S = A_e K1[64 rows]^T is
 // 128x64, and every group has two S and two P buffers, so its next unit is
@@ -54,7 +57,12 @@ using namespace sa2::sm100;
 
 constexpr int TQ = 128;          // query rows per CTA
 constexpr int TJ = 128;          // first-key rows per tile
-constexpr int FWD_THREADS = 320;
+constexpr int FWD_THREADS = 512;
+// Register hand-over between warpgroups (launch: 128 per thread; the budgets must add up to 4 * 128, or
+// the growing group never returns from its setmaxnreg).
+constexpr int FWD_REGS_LAUNCH = 128, FWD_REGS_ISSUE = 56, FWD_REGS_SOFTMAX = 112, FWD_REGS_OUT = 232;
+static_assert(FWD_REGS_ISSUE + 2 * FWD_REGS_SOFTMAX + FWD_REGS_OUT == 4 * FWD_REGS_LAUNCH, "register pool must balance");
+static_assert(FWD_REGS_SOFTMAX < FWD_REGS_LAUNCH, "the softmax groups release registers");
 constexpr int MAX_NT = 5;        // K1/V1 tiles resident in shared memory (head dim 64)
 constexpr uint32_t TILE_BYTES = TJ * 64 * 2;
 constexpr int K2_ROWS = 160;     // second-key rows kept in shared memory: positions i0 - 32 ... i0 + 127
@@ -68,11 +76,13 @@ enum FwdBar {
     BAR_S_FULL = BAR_W_EMPTY + 2,        // [4] group * 2 + buffer
     BAR_P_FULL = BAR_S_FULL + 4,         // [4]
     BAR_PV_DONE = BAR_P_FULL + 4,        // [4]
-    BAR_COUNT = BAR_PV_DONE + 4
+    BAR_A_FREE = BAR_PV_DONE + 4,        // [2] per group: every S product of the sweep has completed
+    BAR_REF_FULL = BAR_A_FREE + 2,       // [2] per group: the sweep's final reference is in shared memory
+    BAR_COUNT = BAR_REF_FULL + 2
 };
 
 // error bits reported through the device status word
-enum { ERR_FWD_PRODUCER = 1, ERR_FWD_MMA = 2, ERR_FWD_SOFTMAX = 4 };
+enum { ERR_FWD_PRODUCER = 1, ERR_FWD_MMA = 2, ERR_FWD_SOFTMAX = 4, ERR_FWD_OUTPUT = 8 };
 
 struct FwdParams {
     KernelParams kp;
@@ -81,9 +91,13 @@ struct FwdParams {
     int *status;     // device status word
 };
 
+// per-row hand-over between a softmax thread and the output thread of its row:
+// [group][sweep parity][128] final reference of the sweep, then [group][128] denominator and
+// [group][128] the reference it is expressed against
+constexpr int FWD_STATS_FLOATS = 2 * 2 * 128 + 2 * 128 + 2 * 128;
 // at least 120 KB: one CTA per SM, so the 512-column TMEM allocation never waits for a co-resident CTA
 inline size_t fwd_smem_bytes(int nt) {
-    const size_t need = 1024 + (size_t)nt * 2 * TILE_BYTES + 2 * TILE_BYTES + K2_ROWS * 128 + 256 + 1024;
+    const size_t need = 1024 + (size_t)nt * 2 * TILE_BYTES + 2 * TILE_BYTES + K2_ROWS * 128 + FWD_STATS_FLOATS * 4 + 256 + 1024;
     return need > 120 * 1024 ? need : 120 * 1024;
 }
 
@@ -196,6 +210,7 @@ __device__ __forceinline__ int fwd_mma(const FwdGeom &g, int grp, uint32_t tmem,
         mma_ss(d, dA + 4, kt + 4, IDESC_S, 1u);
         mma_ss(d, dA + 6, kt + 6, IDESC_S, 1u);
         tc_commit(&bars[BAR_S_FULL + grp * 2 + sb]);
+        if (s_w == g.upe - 1) tc_commit(&bars[BAR_A_FREE + grp]);      // the A stage may be rebuilt
         if (++s_w == g.upe) { s_w = 0; ++s_k; }
         return true;
     };
@@ -228,13 +243,9 @@ __device__ __forceinline__ int fwd_mma(const FwdGeom &g, int grp, uint32_t tmem,
     return 0;
 }
 
-// ------------------------------------------------------------------ warps 2-9
-struct RowState {
-    float ref, l;
-    float o[64];
-};
-
-// probabilities of 32 columns [col0, col0 + 32) of one S buffer -> packed bf16; returns their sum
+// ------------------------------------------------------------------ softmax groups (warps 4-7, 8-11)
+// exp2(c * s - ref) for 32 logits of one row -> 16 packed bf16 pairs; returns their sum.
+// Columns outside (lo, hi] are masked (window / causality / sequence start).
 __device__ __forceinline__ float fwd_probs32(const uint32_t (&s)[32], uint32_t (&pk)[16], float c, float ref,
                                              bool full, int col0, int lo, int hi) {
     float sum0 = 0.f, sum1 = 0.f;
@@ -261,88 +272,24 @@ __device__ __forceinline__ float fwd_probs32(const uint32_t (&s)[32], uint32_t (
     return sum0 + sum1;
 }
 
-__device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g, int grp, uint32_t tmem, RowState &st,
-                                           uint8_t *sA, const uint8_t *sK2, uint64_t *bars, volatile int *abort_flag) {
+__device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g, int grp, uint32_t tmem, float *stats,
+                                           uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = (warp & 3) * 32 + lane;            // query row within the tile = TMEM lane
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t s_addr = lane_addr + grp * 128, p_addr = lane_addr + 384 + grp * 64, w_addr = lane_addr + 256 + grp * 64;
-    const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
     const int i = g.i0 + r;
     const bool row_ok = i < kp.n;
     const float c = P.c;
-    const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p);
     const int nsw = grp == 0 ? (g.nsweeps + 1) / 2 : g.nsweeps / 2;
+    float *ref_slot = stats + grp * 256 + r;          // + 128 * (sweep parity)
 
     float ref = -CUDART_INF_F, l = 0.f;
-    float ref_w_cur = -CUDART_INF_F, ref_w_prev = -CUDART_INF_F;
-    float (&o)[64] = st.o;
-
-    // row r of A_e = q_i * k2_{i-e} for this group's sweep e, into the group's A stage
-    const __nv_bfloat16 *qrow = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, row_ok ? i : 0, h);
-    const bool k2_in_smem = kp.w2 <= 32;
-    auto build_a = [&](int e) {
-        uint8_t *dst = sA + (size_t)grp * TILE_BYTES;
-        const int kk = i + kp.off2 - e;
-        const bool ok = row_ok && kk >= 0;
-        const __nv_bfloat16 *krow = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p) + elem_off(kp.k2, b, ok ? kk : 0, hk);
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (ok) {
-                const uint4 a = __ldg(reinterpret_cast<const uint4 *>(qrow + cc * 8));
-                const uint4 kv = k2_in_smem ? *reinterpret_cast<const uint4 *>(sK2 + sw128_offset(r + 32 - e, cc))
-                                            : __ldg(reinterpret_cast<const uint4 *>(krow + cc * 8));
-                v.x = mul_bf16x2(a.x, kv.x); v.y = mul_bf16x2(a.y, kv.y);
-                v.z = mul_bf16x2(a.z, kv.z); v.w = mul_bf16x2(a.w, kv.w);
-            }
-            *reinterpret_cast<uint4 *>(dst + sw128_offset(r, cc)) = v;
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(&bars[BAR_A_FULL + grp]);
-    };
-    if (!warp_wait(&bars[BAR_K2_FULL], 0, abort_flag)) return ERR_FWD_SOFTMAX;
-    if (nsw > 0) build_a(grp);
-
-    // add v2_{i-e} * W_e (TMEM) into the output registers; ref_w is the reference W_e was built against
-    auto drain = [&](int k, float ref_w) -> bool {
-        if (!warp_wait(&bars[BAR_W_FULL + grp], k & 1, abort_flag)) return false;
-        tc_fence_after();
-        const int kk = i + kp.off2 - (2 * k + grp);
-        const bool ok = row_ok && kk >= 0 && ref_w > -CUDART_INF_F;
-        const float f = ok ? ex2(ref_w - ref) : 0.f;
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            uint32_t w[32];
-            tmem_ld32(w_addr + half * 32, w);
-            tmem_wait_ld();
-            if (ok) {
-                const __nv_bfloat16 *vp = v2 + elem_off(kp.v2, b, kk, hk) + half * 32;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(vp + u * 8));
-                    const uint32_t rr[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                    for (int z = 0; z < 4; ++z) {
-                        const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162 *>(&rr[z]);
-                        const int x = half * 32 + u * 8 + z * 2;
-                        o[x] = fmaf(f * __uint_as_float(w[u * 8 + z * 2]), __low2float(vv), o[x]);
-                        o[x + 1] = fmaf(f * __uint_as_float(w[u * 8 + z * 2 + 1]), __high2float(vv), o[x + 1]);
-                    }
-                }
-            }
-        }
-        tc_fence_before();
-        mbar_arrive(&bars[BAR_W_EMPTY + grp]);
-        return true;
-    };
 
     for (int k = 0; k < nsw; ++k) {
         const int e = 2 * k + grp;
         const bool sweep_ok = row_ok && (i + kp.off2 - e >= 0);
-        ref_w_prev = ref_w_cur;
-        ref_w_cur = ref;
 #pragma unroll 1
         for (int w = 0; w < g.upe; ++w) {
             const int u = k * g.upe + w, sb = u & 1;
@@ -355,8 +302,6 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             if (!warp_wait(&bars[BAR_S_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
             SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 1);
             tc_fence_after();
-            // every S product of this sweep has now completed: the A stage is free for the next sweep
-            if (w == g.upe - 1 && k + 1 < nsw) build_a(e + 2);
             const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
 
             float tile_sum = 0.f;
@@ -388,10 +333,7 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
                     const float nref = mx * c;
                     f = ex2(ref - nref);                       // 0 when ref was -inf
                     l *= f;
-#pragma unroll
-                    for (int x = 0; x < 64; ++x) o[x] *= f;
-                    ref = nref;
-                    ref_w_cur = nref;
+                    ref = nref;     // the output thread rescales its accumulator when it sees the new reference
                 }
                 if (w > 0) {
                     // W of this sweep already holds partial sums against the old reference
@@ -421,20 +363,135 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             l += tile_sum;
             tmem_wait_st();
             SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 2);
-            // the previous sweep's W is folded in here, where its MMAs have long finished
-            if (w == 0 && k >= 1 && !drain(k - 1, ref_w_prev)) return ERR_FWD_SOFTMAX;
+            if (w == g.upe - 1) {
+                // W_e is expressed against the reference the row has now.  The output thread has read the
+                // slot of sweep k - 2 before it released that sweep's W; waiting for the release of sweep
+                // k - 1 also keeps this barrier from running two phases ahead of its reader.
+                if (k >= 1 && !warp_wait(&bars[BAR_W_EMPTY + grp], (k - 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
+                ref_slot[(k & 1) * 128] = ref;
+                mbar_arrive(&bars[BAR_REF_FULL + grp]);
+            }
             tc_fence_before();
             mbar_arrive(&bars[BAR_P_FULL + grp * 2 + sb]);
             SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 3);
         }
     }
-    if (nsw > 0 && !drain(nsw - 1, ref_w_cur)) return ERR_FWD_SOFTMAX;
-    st.ref = ref;
-    st.l = l;
+    stats[512 + grp * 128 + r] = l;
+    stats[768 + grp * 128 + r] = ref;
     return 0;
 }
 
-__device__ __forceinline__ void fwd_groups_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+// ------------------------------------------------------------------ output group (warps 12-15)
+// Thread r owns query row r: it builds row r of every A tile and accumulates the row's output, one
+// accumulator per softmax group, each against the reference that group reported with its last sweep.
+__device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, uint32_t tmem, float (&o0)[64], float (&o1)[64],
+                                          float &ref0, float &ref1, uint8_t *sA, const uint8_t *sK2, const float *stats,
+                                          uint64_t *bars, volatile int *abort_flag) {
+    const KernelParams &kp = P.kp;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
+    const int i = g.i0 + r;
+    const bool row_ok = i < kp.n;
+    const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
+    const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p);
+    const bool k2_in_smem = kp.w2 <= 32;
+    const int nsw0 = (g.nsweeps + 1) / 2, nsw1 = g.nsweeps / 2;
+
+    uint4 qv[8];
+#pragma unroll
+    for (int cc = 0; cc < 8; ++cc) qv[cc] = make_uint4(0u, 0u, 0u, 0u);
+    if (row_ok) {
+        const __nv_bfloat16 *qrow = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, i, h);
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) qv[cc] = __ldg(reinterpret_cast<const uint4 *>(qrow + cc * 8));
+    }
+
+    // row r of A_e = q_i * k2_{i-e} for sweep e = 2 k + grp, into the group's A stage
+    auto build_a = [&](int grp, int k) {
+        const int e = 2 * k + grp;
+        uint8_t *dst = sA + (size_t)grp * TILE_BYTES;
+        const int kk = i + kp.off2 - e;
+        const bool ok = row_ok && kk >= 0;
+        const __nv_bfloat16 *krow = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (ok) {
+                const uint4 kv = k2_in_smem ? *reinterpret_cast<const uint4 *>(sK2 + sw128_offset(r + 32 - e, cc))
+                                            : __ldg(reinterpret_cast<const uint4 *>(krow + cc * 8));
+                v.x = mul_bf16x2(qv[cc].x, kv.x); v.y = mul_bf16x2(qv[cc].y, kv.y);
+                v.z = mul_bf16x2(qv[cc].z, kv.z); v.w = mul_bf16x2(qv[cc].w, kv.w);
+            }
+            *reinterpret_cast<uint4 *>(dst + sw128_offset(r, cc)) = v;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars[BAR_A_FULL + grp]);
+    };
+
+    // o += v2_{i-e} * W_e (TMEM), after moving o to the reference W_e was built against
+    auto drain = [&](int grp, int k, float (&o)[64], float &ref_o) -> bool {
+        if (!warp_wait(&bars[BAR_REF_FULL + grp], k & 1, abort_flag)) return false;
+        const float ref_w = stats[grp * 256 + (k & 1) * 128 + r];
+        if (!warp_wait(&bars[BAR_W_FULL + grp], k & 1, abort_flag)) return false;
+        tc_fence_after();
+        const int kk = i + kp.off2 - (2 * k + grp);
+        const bool ok = row_ok && kk >= 0 && ref_w > -CUDART_INF_F;
+        if (ok && ref_w > ref_o) {
+            const float f = ex2(ref_o - ref_w);              // 0 while the accumulator is still empty
+#pragma unroll
+            for (int x = 0; x < 64; ++x) o[x] *= f;
+            ref_o = ref_w;
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            uint32_t w[32];
+            tmem_ld32(lane_addr + 256 + grp * 64 + half * 32, w);
+            tmem_wait_ld();
+            if (ok) {
+                const __nv_bfloat16 *vp = v2 + elem_off(kp.v2, b, kk, hk) + half * 32;
+                uint4 raw[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) raw[u] = __ldg(reinterpret_cast<const uint4 *>(vp + u * 8));
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t rr[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+                    for (int z = 0; z < 4; ++z) {
+                        const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162 *>(&rr[z]);
+                        const int x = half * 32 + u * 8 + z * 2;
+                        o[x] = fmaf(__uint_as_float(w[u * 8 + z * 2]), __low2float(vv), o[x]);
+                        o[x + 1] = fmaf(__uint_as_float(w[u * 8 + z * 2 + 1]), __high2float(vv), o[x + 1]);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        mbar_arrive(&bars[BAR_W_EMPTY + grp]);
+        return true;
+    };
+
+    if (!warp_wait(&bars[BAR_K2_FULL], 0, abort_flag)) return ERR_FWD_OUTPUT;
+    if (nsw0 > 0) build_a(0, 0);
+    if (nsw1 > 0) build_a(1, 0);
+    for (int k = 0; k < nsw0; ++k) {
+        // the A stages first: the tensor cores wait for them, the W accumulators have a unit's slack
+        if (k + 1 < nsw0) {
+            if (!warp_wait(&bars[BAR_A_FREE + 0], k & 1, abort_flag)) return ERR_FWD_OUTPUT;
+            build_a(0, k + 1);
+        }
+        if (k + 1 < nsw1) {
+            if (!warp_wait(&bars[BAR_A_FREE + 1], k & 1, abort_flag)) return ERR_FWD_OUTPUT;
+            build_a(1, k + 1);
+        }
+        if (!drain(0, k, o0, ref0)) return ERR_FWD_OUTPUT;
+        if (k < nsw1 && !drain(1, k, o1, ref1)) return ERR_FWD_OUTPUT;
+    }
+    return 0;
+}
+
+__device__ __forceinline__ void fwd_rows_sync() { asm volatile("bar.sync 2, 384;" ::: "memory"); }
 
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
@@ -445,8 +502,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
     uint8_t *sV = sK + (size_t)P.nt * TILE_BYTES;
     uint8_t *sA = sV + (size_t)P.nt * TILE_BYTES;
     uint8_t *sK2 = sA + 2 * TILE_BYTES;
-    float *merge_stats = reinterpret_cast<float *>(sK2 + K2_ROWS * 128);       // [2][128]: ref, l of group 1
-    uint64_t *bars = reinterpret_cast<uint64_t *>(merge_stats + 256);
+    float *stats = reinterpret_cast<float *>(sK2 + K2_ROWS * 128);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stats + FWD_STATS_FLOATS);
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + BAR_COUNT);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
 
@@ -454,7 +511,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
     if (threadIdx.x == 0) {
         for (int x = 0; x < BAR_COUNT; ++x) {
             const bool many = (x >= BAR_P_FULL && x < BAR_P_FULL + 4) || (x >= BAR_W_EMPTY && x < BAR_W_EMPTY + 2) ||
-                              (x >= BAR_A_FULL && x < BAR_A_FULL + 2);
+                              (x >= BAR_A_FULL && x < BAR_A_FULL + 2) || (x >= BAR_REF_FULL && x < BAR_REF_FULL + 2);
             mbar_init(&bars[x], many ? 128u : 1u);
         }
         *abort_flag = 0;
@@ -471,63 +528,57 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
     const FwdGeom g = fwd_geom(P);
 
     int err = 0;
-    if (warp == 0) {
+    if (warp < 4) {
+        reg_dealloc<FWD_REGS_ISSUE>();                // one instruction for the whole warpgroup
         if ((threadIdx.x & 31) == 0) {
-            fwd_producer(P, g, &mapK, &mapV, &mapK2, sK, sV, sK2, bars);
-            err = fwd_mma(g, 1, tmem, sK, sV, sA, bars, abort_flag);
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        if ((threadIdx.x & 31) == 0) err = fwd_mma(g, 0, tmem, sK, sV, sA, bars, abort_flag);
-        __syncwarp();
-    } else {
-        const int grp = (warp - 2) >> 2;
-        RowState st;
-#pragma unroll
-        for (int x = 0; x < 64; ++x) st.o[x] = 0.f;
-        st.ref = -CUDART_INF_F;
-        st.l = 0.f;
-        err = fwd_softmax(P, g, grp, tmem, st, sA, sK2, bars, abort_flag);
-
-        // Merge the two groups' states.  After the first barrier every MMA has completed (each
-        // group waited for its last W), so the A stages can be reused as the exchange buffer.
-        // The barriers sit outside fwd_softmax so that a group that gave up still reaches them.
-        const int r = ((warp & 3) * 32) + (threadIdx.x & 31);
-        float *xo = reinterpret_cast<float *>(sA);           // [128][64], 16-byte chunks rotated by row
-        fwd_groups_sync();
-        if (grp == 1) {
-#pragma unroll
-            for (int c4 = 0; c4 < 16; ++c4)
-                *reinterpret_cast<float4 *>(xo + r * 64 + ((c4 + r) & 15) * 4) =
-                    make_float4(st.o[c4 * 4], st.o[c4 * 4 + 1], st.o[c4 * 4 + 2], st.o[c4 * 4 + 3]);
-            merge_stats[r] = st.ref;
-            merge_stats[128 + r] = st.l;
-        }
-        fwd_groups_sync();
-        if (grp == 0) {
-            const KernelParams &kp = P.kp;
-            const int i = g.i0 + r;
-            const float ref1 = merge_stats[r], l1 = merge_stats[128 + r];
-            const float rmax = fmaxf(st.ref, ref1);
-            const float f0 = st.ref > -CUDART_INF_F ? ex2(st.ref - rmax) : 0.f;
-            const float f1 = ref1 > -CUDART_INF_F ? ex2(ref1 - rmax) : 0.f;
-            const float l = st.l * f0 + l1 * f1;
-            if (i < kp.n && err == 0) {
-                const float inv = 1.f / l;
-                __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(kp.out.p) + elem_off(kp.out, blockIdx.z, i, blockIdx.y);
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const float4 a = *reinterpret_cast<const float4 *>(xo + r * 64 + ((2 * u + r) & 15) * 4);
-                    const float4 bq = *reinterpret_cast<const float4 *>(xo + r * 64 + ((2 * u + 1 + r) & 15) * 4);
-                    uint4 v;
-                    v.x = pack_bf16((st.o[u * 8 + 0] * f0 + a.x * f1) * inv, (st.o[u * 8 + 1] * f0 + a.y * f1) * inv);
-                    v.y = pack_bf16((st.o[u * 8 + 2] * f0 + a.z * f1) * inv, (st.o[u * 8 + 3] * f0 + a.w * f1) * inv);
-                    v.z = pack_bf16((st.o[u * 8 + 4] * f0 + bq.x * f1) * inv, (st.o[u * 8 + 5] * f0 + bq.y * f1) * inv);
-                    v.w = pack_bf16((st.o[u * 8 + 6] * f0 + bq.z * f1) * inv, (st.o[u * 8 + 7] * f0 + bq.w * f1) * inv);
-                    *reinterpret_cast<uint4 *>(op + u * 8) = v;
-                }
-                kp.lse[((int64_t)blockIdx.z * kp.hq + blockIdx.y) * kp.n + i] = (rmax + lg2(l)) * 0.6931471805599453f;
+            if (warp == 0) {
+                fwd_producer(P, g, &mapK, &mapV, &mapK2, sK, sV, sK2, bars);
+                err = fwd_mma(g, 1, tmem, sK, sV, sA, bars, abort_flag);
+            } else if (warp == 1) {
+                err = fwd_mma(g, 0, tmem, sK, sV, sA, bars, abort_flag);
             }
+        }
+        __syncwarp();
+    } else if (warp < 12) {
+        reg_dealloc<FWD_REGS_SOFTMAX>();
+        err = fwd_softmax(P, g, (warp - 4) >> 2, tmem, stats, bars, abort_flag);
+        // the barrier sits outside fwd_softmax so that a group that gave up still reaches it
+        fwd_rows_sync();
+    } else {
+        reg_alloc<FWD_REGS_OUT>();
+        float o0[64], o1[64];
+#pragma unroll
+        for (int x = 0; x < 64; ++x) { o0[x] = 0.f; o1[x] = 0.f; }
+        float ref0 = -CUDART_INF_F, ref1 = -CUDART_INF_F;
+        err = fwd_output(P, g, tmem, o0, o1, ref0, ref1, sA, sK2, stats, bars, abort_flag);
+        fwd_rows_sync();                              // both groups' denominators are in shared memory
+
+        // merge the two groups' states: each accumulator is expressed against its group's last reference
+        const KernelParams &kp = P.kp;
+        const int r = ((warp & 3) * 32) + (threadIdx.x & 31);
+        const int i = g.i0 + r;
+        const float l0 = stats[512 + r], l1 = stats[640 + r];
+        const float lref0 = stats[768 + r], lref1 = stats[896 + r];
+        const float rmax = fmaxf(lref0, lref1);
+        const float f0 = lref0 > -CUDART_INF_F ? ex2(lref0 - rmax) : 0.f;
+        const float f1 = lref1 > -CUDART_INF_F ? ex2(lref1 - rmax) : 0.f;
+        const float l = l0 * f0 + l1 * f1;
+        if (i < kp.n && err == 0) {
+            // an accumulator that last saw an older reference than its group's final one is moved to it
+            const float inv = 1.f / l;
+            const float s0 = ref0 > -CUDART_INF_F ? ex2(ref0 - rmax) * inv : 0.f;
+            const float s1 = ref1 > -CUDART_INF_F ? ex2(ref1 - rmax) * inv : 0.f;
+            __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(kp.out.p) + elem_off(kp.out, blockIdx.z, i, blockIdx.y);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                uint4 v;
+                v.x = pack_bf16(o0[u * 8 + 0] * s0 + o1[u * 8 + 0] * s1, o0[u * 8 + 1] * s0 + o1[u * 8 + 1] * s1);
+                v.y = pack_bf16(o0[u * 8 + 2] * s0 + o1[u * 8 + 2] * s1, o0[u * 8 + 3] * s0 + o1[u * 8 + 3] * s1);
+                v.z = pack_bf16(o0[u * 8 + 4] * s0 + o1[u * 8 + 4] * s1, o0[u * 8 + 5] * s0 + o1[u * 8 + 5] * s1);
+                v.w = pack_bf16(o0[u * 8 + 6] * s0 + o1[u * 8 + 6] * s1, o0[u * 8 + 7] * s0 + o1[u * 8 + 7] * s1);
+                *reinterpret_cast<uint4 *>(op + u * 8) = v;
+            }
+            kp.lse[((int64_t)blockIdx.z * kp.hq + blockIdx.y) * kp.n + i] = (rmax + lg2(l)) * 0.6931471805599453f;
         }
     }
     if (err) atomicOr(P.status, err);
