@@ -322,13 +322,17 @@ __device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g,
                             gk[x >> 1] = pack_bf16(p0 * __uint_as_float(dv[x]), p1 * __uint_as_float(dv[x + 1]));
                         }
                     } else {
+                        // valid columns are the integers in [lo, hi]: saturate(half + 1 - |col - mid|) is
+                        // exactly 1 inside and 0 outside (FMA pipe instead of compares and selects on the
+                        // ALU pipe); the exponent is clamped so that a masked-out cell cannot give inf * 0
+                        const float mid = 0.5f * (float)(lo + hi), hwp = 0.5f * (float)(hi - lo) + 1.f;
 #pragma unroll
                         for (int x = 0; x < 32; x += 2) {
                             const int col = ch * 32 + x;
-                            float p0 = ex2(__uint_as_float(sv[x]) * c);
-                            float p1 = ex2(__uint_as_float(sv[x + 1]) * c);
-                            p0 = (col >= lo && col <= hi) ? p0 : 0.f;
-                            p1 = (col + 1 >= lo && col + 1 <= hi) ? p1 : 0.f;
+                            const float v0 = __saturatef(hwp - fabsf((float)col - mid));
+                            const float v1 = __saturatef(hwp - fabsf((float)(col + 1) - mid));
+                            const float p0 = ex2(fminf(__uint_as_float(sv[x]) * c, 100.f)) * v0;
+                            const float p1 = ex2(fminf(__uint_as_float(sv[x + 1]) * c, 100.f)) * v1;
                             pk[x >> 1] = pack_bf16(p0, p1);
                             gk[x >> 1] = pack_bf16(p0 * __uint_as_float(dv[x]), p1 * __uint_as_float(dv[x + 1]));
                         }

@@ -257,17 +257,29 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
                 tmem_ld32(lane_addr + half * 128 + ch * 32, sv);
                 tmem_ld32(lane_addr + half * 128 + 64 + ch * 32, dv);
                 tmem_wait_ld();
+                if (full) {
 #pragma unroll
-                for (int x = 0; x < 32; x += 2) {
-                    float p0 = ex2(fmaf(__uint_as_float(sv[x]), c, -lse2));
-                    float p1 = ex2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
-                    if (!full) {
-                        const int col = ch * 32 + x;
-                        p0 = (col > lo && col <= hi) ? p0 : 0.f;
-                        p1 = (col + 1 > lo && col + 1 <= hi) ? p1 : 0.f;
+                    for (int x = 0; x < 32; x += 2) {
+                        const float p0 = ex2(fmaf(__uint_as_float(sv[x]), c, -lse2));
+                        const float p1 = ex2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
+                        pp[x >> 1] = pack_bf16(p0, p1);
+                        gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
                     }
-                    pp[x >> 1] = pack_bf16(p0, p1);
-                    gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
+                } else {
+                    // valid columns are the integers in (lo, hi]: saturate(half + 1 - |col - mid|) is exactly 1
+                    // inside and 0 outside (FMA pipe instead of compares and selects on the ALU pipe); the
+                    // exponent is clamped so that a masked-out cell cannot give inf * 0
+                    const float mid = 0.5f * (float)(lo + 1 + hi), hwp = 0.5f * (float)(hi - lo - 1) + 1.f;
+#pragma unroll
+                    for (int x = 0; x < 32; x += 2) {
+                        const int col = ch * 32 + x;
+                        const float v0 = __saturatef(hwp - fabsf((float)col - mid));
+                        const float v1 = __saturatef(hwp - fabsf((float)(col + 1) - mid));
+                        const float p0 = ex2(fminf(fmaf(__uint_as_float(sv[x]), c, -lse2), 100.f)) * v0;
+                        const float p1 = ex2(fminf(fmaf(__uint_as_float(sv[x + 1]), c, -lse2), 100.f)) * v1;
+                        pp[x >> 1] = pack_bf16(p0, p1);
+                        gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
+                    }
                 }
                 // P / G chunk over columns of S / dP that have already been read
                 tmem_st16(lane_addr + half * 128 + ch * 16, pp);

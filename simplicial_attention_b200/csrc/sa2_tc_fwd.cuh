@@ -17,12 +17,12 @@
 //                 then issues the tcgen05.mma stream of group 1 (one lane)
 //   warp 1        owns the TMEM allocation, issues the tcgen05.mma stream of group 0
 //   warps 2-3     idle (they fill the issuers' warpgroup)
-//   warps 4-7     softmax group 0: even sweeps, one thread per query row
-//   warps 8-11    softmax group 1: odd sweeps, one thread per query row
-//   warps 12-15   output group, one thread per query row: builds the A tile of each
+//   warps 4-7     output group, one thread per query row: builds the A tile of each
 //                 group's next sweep as soon as the last S product of its current sweep
 //                 has completed, and at the end of a sweep adds v2_{i-e} * W_e to the
 //                 row's output registers (one accumulator per softmax group)
+//   warps 8-11    softmax group 0: even sweeps, one thread per query row
+//   warps 12-15   softmax group 1: odd sweeps, one thread per query row
 // An even and an odd sweep are in flight together, so while one group runs the
 // exponentials of its tile the tensor cores work for the other and each SM
 // sub-partition has two softmax warps to hide latencies.  A softmax thread keeps
@@ -243,7 +243,7 @@ __device__ __forceinline__ int fwd_mma(const FwdGeom &g, int grp, uint32_t tmem,
     return 0;
 }
 
-// ------------------------------------------------------------------ softmax groups (warps 4-7, 8-11)
+// ------------------------------------------------------------------ softmax groups (warps 8-11, 12-15)
 // exp2(c * s - ref) for 32 logits of one row -> 16 packed bf16 pairs; returns their sum.
 // Columns outside (lo, hi] are masked (window / causality / sequence start).
 __device__ __forceinline__ float fwd_probs32(const uint32_t (&s)[32], uint32_t (&pk)[16], float c, float ref,
@@ -258,13 +258,18 @@ __device__ __forceinline__ float fwd_probs32(const uint32_t (&s)[32], uint32_t (
             pk[x >> 1] = pack_bf16(p0, p1);
         }
     } else {
+        // Valid columns are the integers in (lo, hi]: |col - mid| <= half, and an invalid column is at least
+        // half + 1 away, so saturate(half + 1 - |col - mid|) is exactly 1 or 0: two FADDs and an FMUL on the
+        // FMA pipe instead of two compares and a select on the (half as wide) ALU pipe.  The exponent is
+        // clamped so that a masked-out logit far above the reference cannot produce inf * 0; a clamped
+        // valid logit still trips the slow path.
+        const float mid = 0.5f * (float)(lo + 1 + hi), hwp = 0.5f * (float)(hi - lo - 1) + 1.f;
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-            const int col = col0 + x;
-            float p0 = ex2(fmaf(__uint_as_float(s[x]), c, -ref));
-            float p1 = ex2(fmaf(__uint_as_float(s[x + 1]), c, -ref));
-            p0 = (col > lo && col <= hi) ? p0 : 0.f;
-            p1 = (col + 1 > lo && col + 1 <= hi) ? p1 : 0.f;
+            const float v0 = __saturatef(hwp - fabsf((float)(col0 + x) - mid));
+            const float v1 = __saturatef(hwp - fabsf((float)(col0 + x + 1) - mid));
+            const float p0 = ex2(fminf(fmaf(__uint_as_float(s[x]), c, -ref), 100.f)) * v0;
+            const float p1 = ex2(fminf(fmaf(__uint_as_float(s[x + 1]), c, -ref), 100.f)) * v1;
             sum0 += p0; sum1 += p1;
             pk[x >> 1] = pack_bf16(p0, p1);
         }
@@ -381,7 +386,7 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
     return 0;
 }
 
-// ------------------------------------------------------------------ output group (warps 12-15)
+// ------------------------------------------------------------------ output group (warps 4-7)
 // Thread r owns query row r: it builds row r of every A tile and accumulates the row's output, one
 // accumulator per softmax group, each against the reference that group reported with its last sweep.
 __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, uint32_t tmem, float (&o0)[64], float (&o1)[64],
@@ -410,31 +415,40 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
 
     // row r of A_e = q_i * k2_{i-e} for sweep e = 2 k + grp, into the group's A stage
     auto build_a = [&](int grp, int k) {
+        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8);
         const int e = 2 * k + grp;
         uint8_t *dst = sA + (size_t)grp * TILE_BYTES;
         const int kk = i + kp.off2 - e;
         const bool ok = row_ok && kk >= 0;
         const __nv_bfloat16 *krow = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+        // all eight loads first, then the products and stores
+        uint4 kv[8];
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc)
+            kv[cc] = !ok ? make_uint4(0u, 0u, 0u, 0u)
+                         : k2_in_smem ? *reinterpret_cast<const uint4 *>(sK2 + sw128_offset(r + 32 - e, cc))
+                                      : __ldg(reinterpret_cast<const uint4 *>(krow + cc * 8));
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (ok) {
-                const uint4 kv = k2_in_smem ? *reinterpret_cast<const uint4 *>(sK2 + sw128_offset(r + 32 - e, cc))
-                                            : __ldg(reinterpret_cast<const uint4 *>(krow + cc * 8));
-                v.x = mul_bf16x2(qv[cc].x, kv.x); v.y = mul_bf16x2(qv[cc].y, kv.y);
-                v.z = mul_bf16x2(qv[cc].z, kv.z); v.w = mul_bf16x2(qv[cc].w, kv.w);
-            }
+            uint4 v;
+            v.x = mul_bf16x2(qv[cc].x, kv[cc].x); v.y = mul_bf16x2(qv[cc].y, kv[cc].y);
+            v.z = mul_bf16x2(qv[cc].z, kv[cc].z); v.w = mul_bf16x2(qv[cc].w, kv[cc].w);
             *reinterpret_cast<uint4 *>(dst + sw128_offset(r, cc)) = v;
         }
+        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 7);
         fence_proxy_async_smem();
         mbar_arrive(&bars[BAR_A_FULL + grp]);
+        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 1);
     };
 
     // o += v2_{i-e} * W_e (TMEM), after moving o to the reference W_e was built against
     auto drain = [&](int grp, int k, float (&o)[64], float &ref_o) -> bool {
+        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 2);
         if (!warp_wait(&bars[BAR_REF_FULL + grp], k & 1, abort_flag)) return false;
+        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 3);
         const float ref_w = stats[grp * 256 + (k & 1) * 128 + r];
         if (!warp_wait(&bars[BAR_W_FULL + grp], k & 1, abort_flag)) return false;
+        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 4);
         tc_fence_after();
         const int kk = i + kp.off2 - (2 * k + grp);
         const bool ok = row_ok && kk >= 0 && ref_w > -CUDART_INF_F;
@@ -469,6 +483,7 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
         }
         tc_fence_before();
         mbar_arrive(&bars[BAR_W_EMPTY + grp]);
+        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 5);
         return true;
     };
 
@@ -478,10 +493,12 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
     for (int k = 0; k < nsw0; ++k) {
         // the A stages first: the tensor cores wait for them, the W accumulators have a unit's slack
         if (k + 1 < nsw0) {
+            SA2_TRACE_MARK(r == 0, 6000 + ((k + 1) * 2 + 0) * 8 + 6);
             if (!warp_wait(&bars[BAR_A_FREE + 0], k & 1, abort_flag)) return ERR_FWD_OUTPUT;
             build_a(0, k + 1);
         }
         if (k + 1 < nsw1) {
+            SA2_TRACE_MARK(r == 0, 6000 + ((k + 1) * 2 + 1) * 8 + 6);
             if (!warp_wait(&bars[BAR_A_FREE + 1], k & 1, abort_flag)) return ERR_FWD_OUTPUT;
             build_a(1, k + 1);
         }
@@ -539,9 +556,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
             }
         }
         __syncwarp();
-    } else if (warp < 12) {
+    } else if (warp >= 8) {
         reg_dealloc<FWD_REGS_SOFTMAX>();
-        err = fwd_softmax(P, g, (warp - 4) >> 2, tmem, stats, bars, abort_flag);
+        err = fwd_softmax(P, g, (warp - 8) >> 2, tmem, stats, bars, abort_flag);
         // the barrier sits outside fwd_softmax so that a group that gave up still reaches it
         fwd_rows_sync();
     } else {
