@@ -15,6 +15,7 @@ from __future__ import annotations
 from functools import partial
 from typing import Callable
 
+import torch
 from torch.nn import Identity, Linear, Module, ModuleList, RMSNorm
 
 from .attention import divisible_by, exists, sliding_two_simplicial_attn
@@ -86,7 +87,8 @@ class HigherOrderAttention(Module):
         t = t.view(b, n, heads, -1)
         return t.transpose(1, 2) if self.head_first_dim else t
 
-    def forward(self, tokens):
+    def _project(self, tokens):
+        """tokens -> (queries, keys, values) after the head split and the per-head norms."""
         tokens = self.prenorm(tokens)
         q, k, v = self.to_qkv(tokens).split(self.split_dims, dim=-1)
 
@@ -99,13 +101,17 @@ class HigherOrderAttention(Module):
             queries = self.q_norm(queries)
             keys = tuple(norm(t) for norm, t in zip(self.k_norms, keys))
             values = tuple(norm(t) for norm, t in zip(self.v_norms, values))
+        return queries, keys, values
 
-        out = self.attend(queries, keys, values)
-
+    def _merge(self, out):
         if self.head_first_dim:
             out = out.transpose(1, 2)
         out = out.reshape(out.shape[0], out.shape[1], -1)
         return self.postnorm(self.combine_heads(out))
+
+    def forward(self, tokens):
+        queries, keys, values = self._project(tokens)
+        return self._merge(self.attend(queries, keys, values))
 
 
 class SlidingWindowTwoSimplicialMHA(HigherOrderAttention):
@@ -115,3 +121,21 @@ class SlidingWindowTwoSimplicialMHA(HigherOrderAttention):
         attend = partial(sliding_two_simplicial_attn, w1=w1, w2=w2, causal=True)
         super().__init__(*args, number_key_value_sets=2, head_first_dim=False, attend=attend, **kwargs)
         self.w1, self.w2 = w1, w2
+
+    def forward(self, tokens, cache=None, return_cache=False):
+        """``cache`` (from an earlier call with ``return_cache=True``) holds the last ``w1 - 1`` rows of the
+        first key/value set and the last ``w2 - 1`` rows of the second: all a later token can still see.
+        With a cache, ``tokens`` are only the new positions; the cached rows ride in front of the new keys
+        as the halo the kernels already understand, so decoding a token costs one window, not the prefix
+        (the reference's sampling loop re-runs the whole prefix for every token, train.py:103-104)."""
+        queries, keys, values = self._project(tokens)
+        if cache is not None:
+            keys = tuple(torch.cat((c, t), dim=1) for c, t in zip(cache[0], keys))
+            values = tuple(torch.cat((c, t), dim=1) for c, t in zip(cache[1], values))
+        out = self._merge(self.attend(queries, keys, values))
+        if not return_cache:
+            return out
+        keep = (self.w1 - 1, self.w2 - 1)
+        new_cache = (tuple(t[:, t.shape[1] - min(k, t.shape[1]):].detach() for t, k in zip(keys, keep)),
+                     tuple(t[:, t.shape[1] - min(k, t.shape[1]):].detach() for t, k in zip(values, keep)))
+        return out, new_cache

@@ -12,6 +12,8 @@ layers use torch's scaled-dot-product attention, as in the reference.
 """
 from __future__ import annotations
 
+import math
+
 import torch
 import torch.nn.functional as F
 from torch import nn
@@ -33,15 +35,20 @@ class Attention(Module):
         self.to_kv = nn.Linear(dim, key_value_heads * dim_head * 2, bias=False)
         self.to_out = nn.Linear(heads * dim_head, dim, bias=False)
 
-    def forward(self, x):
+    def forward(self, x, cache=None, return_cache=False):
+        """``cache`` = (keys, values) of every earlier position; with a cache ``x`` is one new position."""
         b, n, _ = x.shape
         x = self.prenorm(x)
         q = self.to_q(x).view(b, n, self.heads, self.dim_head).transpose(1, 2)
         # the fused projection is laid out (kv, h, d), as in the reference's rearrange
         kv = self.to_kv(x).view(b, n, 2, self.key_value_heads, self.dim_head)
         k, v = kv[:, :, 0].transpose(1, 2), kv[:, :, 1].transpose(1, 2)
-        out = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.heads != self.key_value_heads)
-        return self.to_out(out.transpose(1, 2).reshape(b, n, -1))
+        if cache is not None:
+            assert n == 1, "with a cache, feed one new position at a time"
+            k, v = torch.cat((cache[0], k), dim=2), torch.cat((cache[1], v), dim=2)
+        out = F.scaled_dot_product_attention(q, k, v, is_causal=cache is None, enable_gqa=self.heads != self.key_value_heads)
+        out = self.to_out(out.transpose(1, 2).reshape(b, n, -1))
+        return (out, (k.detach(), v.detach())) if return_cache else out
 
 
 def FeedForward(dim, expansion=4.0):
@@ -65,11 +72,20 @@ class TwoSimplicialTransformer(Module):
         self.layers = ModuleList(layers)
         self.norm = nn.RMSNorm(dim) if final_norm else nn.Identity()
 
-    def forward(self, x):
-        for attn, ff in self.layers:
-            x = attn(x) + x
+    def forward(self, x, cache=None, return_cache=False):
+        """``cache``: one entry per layer, as returned by an earlier call with ``return_cache=True``."""
+        if cache is None and not return_cache:
+            for attn, ff in self.layers:
+                x = attn(x) + x
+                x = ff(x) + x
+            return self.norm(x)
+        new_cache = []
+        for index, (attn, ff) in enumerate(self.layers):
+            a, c = attn(x, cache=None if cache is None else cache[index], return_cache=True)
+            new_cache.append(c)
+            x = a + x
             x = ff(x) + x
-        return self.norm(x)
+        return self.norm(x), new_cache
 
 
 class TwoSimplicialLM(Module):
@@ -87,15 +103,46 @@ class TwoSimplicialLM(Module):
                                                     **transformer_kwargs)
         self.to_logits = nn.Linear(dim, num_tokens, bias=False)
 
-    def forward(self, x, return_loss=False):
+    def forward(self, x, return_loss=False, cache=None, return_cache=False):
         if return_loss:
             x, target = x[:, :-1], x[:, 1:]
         n = x.shape[-1]
-        tokens = self.token_emb(x) + self.pos_emb(torch.arange(n, device=x.device))
-        logits = self.to_logits(self.transformer(tokens))
+        start = 0 if cache is None else cache["length"]
+        tokens = self.token_emb(x) + self.pos_emb(torch.arange(start, start + n, device=x.device))
+        if cache is None and not return_cache:
+            logits = self.to_logits(self.transformer(tokens))
+        else:
+            embed, layers = self.transformer(tokens, cache=None if cache is None else cache["layers"], return_cache=True)
+            logits = self.to_logits(embed)
+            return logits, {"length": start + n, "layers": layers}
         if not return_loss:
             return logits
         return F.cross_entropy(logits.transpose(1, 2), target)
+
+    @torch.no_grad()
+    def sample(self, prompt: torch.Tensor, seq_len: int, temperature=1.0, filter_thres=0.9, use_cache=True):
+        """Same contract as the reference's ``sample`` (train.py:92-111): top-k filtered Gumbel sampling
+        until ``seq_len`` tokens, returning only the generated part.  With ``use_cache`` the prompt is run
+        once and every further token costs one position: the standard layers keep their keys and values,
+        the simplicial layers only their ``w1 - 1`` / ``w2 - 1`` row windows."""
+        out = prompt.clone()
+        steps = max(0, seq_len - prompt.shape[-1])
+        cache = None
+        for step in range(steps):
+            if not use_cache:
+                logits = self.forward(out)
+            elif cache is None:
+                logits, cache = self.forward(out, return_cache=True)
+            else:
+                logits, cache = self.forward(out[:, -1:], cache=cache, return_cache=True)
+            logits = logits[:, -1].float()
+            k = max(1, math.ceil((1 - filter_thres) * logits.shape[-1]))
+            val, ind = torch.topk(logits, k)
+            kept = torch.full_like(logits, float("-inf")).scatter_(-1, ind, val)
+            noise = -torch.log(-torch.log(torch.rand_like(kept).clamp_min(1e-20)).clamp_min(1e-20))
+            nxt = (kept / max(temperature, 1e-10) + noise).argmax(dim=-1, keepdim=True)
+            out = torch.cat((out, nxt), dim=-1)
+        return out[..., prompt.shape[-1]:]
 
 
 def training_step(model: Module, optimizer: torch.optim.Optimizer, tokens: torch.Tensor, max_grad_norm=0.5) -> torch.Tensor:

@@ -43,3 +43,52 @@ def test_training_steps_reduce_the_loss():
             losses.append(training_step(model, opt, tokens).item())
     assert all(l == l for l in losses)                  # finite
     assert losses[-1] < losses[0] - 0.3, losses         # memorises the fixed batch
+
+
+def test_standard_attention_cache_matches_full_pass():
+    from simplicial_attention_b200.transformer import Attention
+
+    torch.manual_seed(1)
+    layer = Attention(dim=64, dim_head=16, heads=4, key_value_heads=2)
+    x = torch.randn(2, 9, 64)
+    full = layer(x)
+    out, cache = layer(x[:, :6], return_cache=True)
+    steps = [out]
+    for t in range(6, 9):
+        o, cache = layer(x[:, t:t + 1], cache=cache, return_cache=True)
+        steps.append(o)
+    assert torch.allclose(torch.cat(steps, dim=1), full, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_cached_decoding_matches_full_prefix():
+    # fp32 weights and activations: the simplicial layers run the fp32 kernels, so the cached path
+    # (window rows carried as a halo) must agree with re-running the whole prefix
+    torch.manual_seed(2)
+    model = _lm().cuda().eval()
+    tokens = torch.randint(0, 256, (2, 40), device="cuda")      # longer than both windows (16, 4)
+    with torch.no_grad():
+        full = model(tokens)
+        logits, cache = model(tokens[:, :21], return_cache=True)
+        got = [logits]
+        for t in range(21, 40):
+            step, cache = model(tokens[:, t:t + 1], cache=cache, return_cache=True)
+            got.append(step)
+    got = torch.cat(got, dim=1)
+    assert (got - full).abs().max().item() <= 1e-3 * full.abs().max().item()
+    # the simplicial layers keep windows, not the prefix
+    k1_rows = cache["layers"][1][0][0].shape[1]
+    k2_rows = cache["layers"][1][0][1].shape[1]
+    assert (k1_rows, k2_rows) == (15, 3)
+
+
+@pytest.mark.gpu
+def test_sample_with_and_without_cache():
+    torch.manual_seed(3)
+    model = _lm().cuda().eval()
+    prompt = torch.randint(0, 256, (2, 10), device="cuda")
+    torch.manual_seed(7)
+    a = model.sample(prompt, 30, temperature=1e-6, filter_thres=0.99, use_cache=True)
+    torch.manual_seed(7)
+    b = model.sample(prompt, 30, temperature=1e-6, filter_thres=0.99, use_cache=False)
+    assert a.shape == (2, 20) and torch.equal(a, b)              # greedy: identical continuations
