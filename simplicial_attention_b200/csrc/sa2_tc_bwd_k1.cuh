@@ -37,18 +37,23 @@ namespace sa2 {
 namespace tc {
 
 constexpr int BK1_THREADS = 448;
+// A_e / B_e stages.  A stage is released only when the second products of its step have completed, i.e.
+// after build -> first products -> P^T/G^T pass -> second products; with two stages the builders (whose
+// 32 shared-memory accesses per step take ~1600 cycles next to the tensor cores' operand traffic) waited
+// for that chain every step and paced the kernel at ~3000 cycles per step.
+constexpr int BK1_STAGES = 3;
 
 enum Bk1Bar {
     BK1_KV_FULL = 0,
-    BK1_AB_FULL = 1,     // [2]
-    BK1_AB_EMPTY = 3,    // [2]
-    BK1_S_FULL = 5,      // [2] per half
-    BK1_P_FULL = 7,      // [2] per half
-    BK1_G_DONE = 9,      // [2] per half: second products of the step have completed
-    BK1_DONE = 11,
-    BK1_WIN_FREE = 12,   // the builders have finished reading the k2/v2 window of the previous query tile
-    BK1_WIN_FULL = 13,   // the window of the current query tile has landed
-    BK1_BAR_COUNT = 14
+    BK1_AB_FULL = 1,     // [BK1_STAGES]
+    BK1_AB_EMPTY = 4,    // [BK1_STAGES]
+    BK1_S_FULL = 7,      // [2] per half
+    BK1_P_FULL = 9,      // [2] per half
+    BK1_G_DONE = 11,     // [2] per half: second products of the step have completed
+    BK1_DONE = 13,
+    BK1_WIN_FREE = 14,   // the builders have finished reading the k2/v2 window of the previous query tile
+    BK1_WIN_FULL = 15,   // the window of the current query tile has landed
+    BK1_BAR_COUNT = 16
 };
 
 enum { ERR_BK1_PRODUCER = 16, ERR_BK1_MMA = 32, ERR_BK1_COMPUTE = 64, ERR_BK1_BUILDER = 128 };
@@ -62,7 +67,7 @@ struct BwdParams {
 // padded above half of the SM's shared memory: one CTA per SM, so the 512-column TMEM allocation never waits
 constexpr int BK1_WIN_ROWS = 160;    // second-key / second-value rows a query tile can pair with: 32 + 128
 inline size_t bk1_smem_bytes() {
-    return 1024 + 2 * TILE_BYTES + 4 * TILE_BYTES + 4 * TILE_BYTES + TILE_BYTES + 2 * BK1_WIN_ROWS * 128 + 256;
+    return 1024 + 2 * TILE_BYTES + BK1_STAGES * 2 * TILE_BYTES + 2 * TILE_BYTES + TILE_BYTES + 2 * BK1_WIN_ROWS * 128 + 256;
 }
 
 struct Bk1Geom {
@@ -157,18 +162,20 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
                 dl = kp.delta[o];
             }
             for (int e = 0; e < ne; ++e, ++s) {
-                const int stage = s & 1;
+                const int stage = s % BK1_STAGES;
                 SA2_TRACE_MARK(r == 0 && s < 200, s * 4);
-                if (s >= 2 && !warp_wait(&bars[BK1_AB_EMPTY + stage], ((s >> 1) - 1) & 1, abort_flag)) return ERR_BK1_BUILDER;
+                if (s >= BK1_STAGES && !warp_wait(&bars[BK1_AB_EMPTY + stage], (s / BK1_STAGES - 1) & 1, abort_flag)) return ERR_BK1_BUILDER;
                 SA2_TRACE_MARK(r == 0 && s < 200, s * 4 + 1);
                 if (e == 0) {
-                    // statistics of this query tile (first 16 channels of two extra tiles); the buffer of
-                    // two tiles ago is no longer read
-                    uint8_t *stL = sStat + (size_t)(tile_counter & 1) * 2 * TILE_BYTES, *stD = stL + TILE_BYTES;
-                    *reinterpret_cast<uint4 *>(stL + sw128_offset(r, 0)) = split3_bf16(-lse2 * inv_c);
-                    *reinterpret_cast<uint4 *>(stL + sw128_offset(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
-                    *reinterpret_cast<uint4 *>(stD + sw128_offset(r, 0)) = split3_bf16(-dl);
-                    *reinterpret_cast<uint4 *>(stD + sw128_offset(r, 1)) = make_uint4(0u, 0u, 0u, 0u);
+                    // Statistics of this query tile: two K = 16 slabs (-lse2/c, -D) of a four-slab tile; two
+                    // such tiles hold the last four query tiles.  Step s - 3 has completed, and every tile has
+                    // at least one step, so the slabs of four tiles ago are no longer read.
+                    uint8_t *st = sStat + (size_t)((tile_counter >> 1) & 1) * TILE_BYTES;
+                    const int c0 = (tile_counter & 1) * 4;
+                    *reinterpret_cast<uint4 *>(st + sw128_offset(r, c0)) = split3_bf16(-lse2 * inv_c);
+                    *reinterpret_cast<uint4 *>(st + sw128_offset(r, c0 + 1)) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4 *>(st + sw128_offset(r, c0 + 2)) = split3_bf16(-dl);
+                    *reinterpret_cast<uint4 *>(st + sw128_offset(r, c0 + 3)) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 uint8_t *dA = sAB + (size_t)stage * 2 * TILE_BYTES;
                 uint8_t *dB = dA + TILE_BYTES;
@@ -215,17 +222,18 @@ __device__ __forceinline__ int bk1_mma_first(const KernelParams &kp, const Bk1Ge
     for (int hh = 0; hh < kp.g; ++hh) {
         for (int t = 0; t < g.n_it; ++t, ++tile_counter) {
             const int ne = bk1_sweeps(kp, g, t);
-            const uint64_t stL0 = dSt + (uint64_t)(((tile_counter & 1) * 2 * TILE_BYTES) >> 4);
+            // slab (16 channels = 32 bytes = 2 descriptor units) of the statistics tile that holds this query tile
+            const uint64_t stL0 = dSt + (uint64_t)((((tile_counter >> 1) & 1) * TILE_BYTES) >> 4) + (uint64_t)((tile_counter & 1) * 4);
             for (int e = 0; e < ne; ++e, ++s) {
-                const int stage = s & 1;
-                if (!mbar_wait(&bars[BK1_AB_FULL + stage], (s >> 1) & 1, abort_flag)) return ERR_BK1_MMA;
+                const int stage = s % BK1_STAGES;
+                if (!mbar_wait(&bars[BK1_AB_FULL + stage], (s / BK1_STAGES) & 1, abort_flag)) return ERR_BK1_MMA;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     // the compute group must have read the previous step's S^T / dP^T of this half
                     if (s >= 1 && !mbar_wait(&bars[BK1_P_FULL + half], (s - 1) & 1, abort_flag)) return ERR_BK1_MMA;
                     tc_fence_after();
                     const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4), bq = a + (TILE_BYTES >> 4);
-                    const uint64_t stL = stL0 + (uint64_t)((half * 8192) >> 4), stD = stL + (TILE_BYTES >> 4);
+                    const uint64_t stL = stL0 + (uint64_t)((half * 8192) >> 4), stD = stL + 2;
                     const uint32_t d = tmem + half * 128;
                     mma_ss(d, dK, a, IDESC_F, 0u);
                     mma_ss(d, dK + 2, a + 2, IDESC_F, 1u);
@@ -250,7 +258,7 @@ __device__ __forceinline__ int bk1_mma_second(const Bk1Geom &g, uint32_t tmem, u
     constexpr uint32_t IDESC_G = idesc_bf16(128, 64, false, true);    // B operand MN-major
     const uint64_t dAB = smem_desc_sw128(smem_u32(sAB));
     for (int s = 0; s < g.total; ++s) {
-        const int stage = s & 1;
+        const int stage = s % BK1_STAGES;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             SA2_TRACE_MARK(s < 200, 3000 + (s * 2 + half) * 4);
@@ -379,9 +387,9 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sK = smem;
     uint8_t *sV = sK + TILE_BYTES;
-    uint8_t *sAB = sV + TILE_BYTES;                       // 2 stages x (A tile, B tile)
-    uint8_t *sStat = sAB + 4 * TILE_BYTES;                // 2 buffers x (-lse2/c tile, -D tile), 16 channels used
-    uint8_t *sOnes = sStat + 4 * TILE_BYTES;              // constant: three ones per row
+    uint8_t *sAB = sV + TILE_BYTES;                       // BK1_STAGES x (A tile, B tile)
+    uint8_t *sStat = sAB + BK1_STAGES * 2 * TILE_BYTES;   // 2 tiles x 2 query tiles x (-lse2/c slab, -D slab)
+    uint8_t *sOnes = sStat + 2 * TILE_BYTES;              // constant: three ones per row
     uint8_t *sWin = sOnes + TILE_BYTES;                   // staged k2 rows, then v2 rows (160 x 128 B each)
     uint64_t *bars = reinterpret_cast<uint64_t *>(sWin + 2 * BK1_WIN_ROWS * 128);
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + BK1_BAR_COUNT);
@@ -390,7 +398,7 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int x = 0; x < BK1_BAR_COUNT; ++x) {
-            const bool many = (x >= BK1_AB_FULL && x < BK1_AB_FULL + 2) || (x >= BK1_P_FULL && x < BK1_P_FULL + 2) ||
+            const bool many = (x >= BK1_AB_FULL && x < BK1_AB_FULL + BK1_STAGES) || (x >= BK1_P_FULL && x < BK1_P_FULL + 2) ||
                               x == BK1_WIN_FREE;
             mbar_init(&bars[x], many ? 128u : 1u);
         }
