@@ -21,7 +21,7 @@
 // of ones on the key side adds them with one more K=16 MMA, so that the accumulators already hold
 // S^T - lse2 / c and dP^T - D and the compute threads need no per-column loads.
 //
-// Warps (448 threads): 0 TMA producer, then issuer of the second products (dV1, dK1);
+// Warps (480 threads; warp 14 issues dP^T next to warp 1, which issues S^T): 0 TMA producer, then issuer of the second products (dV1, dK1);
 // 1 TMEM owner and issuer of the first products (S^T, dP^T); 2-5 compute group of
 // half 0; 6-9 compute group of half 1; 10-13 builders.  One thread issues about one
 // tcgen05.mma per 90 cycles, so the two products have an issuing thread each; dK1/dV1
@@ -36,7 +36,7 @@
 namespace sa2 {
 namespace tc {
 
-constexpr int BK1_THREADS = 448;
+constexpr int BK1_THREADS = 480;
 // A_e / B_e stages.  A stage is released only when the second products of its step have completed, i.e.
 // after build -> first products -> P^T/G^T pass -> second products; with two stages the builders (whose
 // 32 shared-memory accesses per step take ~1600 cycles next to the tensor cores' operand traffic) waited
@@ -211,11 +211,16 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
 }
 
 // ---------------------------------------------------------------- issuer of S^T, dP^T (warp 1, one lane)
-__device__ __forceinline__ int bk1_mma_first(const KernelParams &kp, const Bk1Geom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV,
+// which = 0: S^T = K1 A_e^T - lse2 / c into columns [128 half, +64) (warp 1);
+// which = 1: dP^T = V1 B_e^T - D into columns [128 half + 64, +64) (warp 14).
+// The two products have an issuing thread each: the time from "the compute group has read the buffer" to
+// "the next S^T / dP^T are complete" is on the critical chain of every step, and one thread issues only
+// one tcgen05.mma per 60-100 cycles.
+__device__ __forceinline__ int bk1_mma_first(const KernelParams &kp, const Bk1Geom &g, int which, uint32_t tmem, uint8_t *sKV,
                                              uint8_t *sAB, uint8_t *sStat, uint8_t *sOnes, uint64_t *bars, volatile int *abort_flag) {
     constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);
-    const uint64_t dK = smem_desc_sw128(smem_u32(sK)), dV = smem_desc_sw128(smem_u32(sV));
-    const uint64_t dAB = smem_desc_sw128(smem_u32(sAB));
+    const uint64_t dT = smem_desc_sw128(smem_u32(sKV));
+    const uint64_t dAB = smem_desc_sw128(smem_u32(sAB + which * TILE_BYTES));
     const uint64_t dSt = smem_desc_sw128(smem_u32(sStat)), dOnes = smem_desc_sw128(smem_u32(sOnes));
     if (!mbar_wait(&bars[BK1_KV_FULL], 0, abort_flag)) return ERR_BK1_MMA;
     int s = 0, tile_counter = 0;
@@ -232,19 +237,14 @@ __device__ __forceinline__ int bk1_mma_first(const KernelParams &kp, const Bk1Ge
                     // the compute group must have read the previous step's S^T / dP^T of this half
                     if (s >= 1 && !mbar_wait(&bars[BK1_P_FULL + half], (s - 1) & 1, abort_flag)) return ERR_BK1_MMA;
                     tc_fence_after();
-                    const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4), bq = a + (TILE_BYTES >> 4);
-                    const uint64_t stL = stL0 + (uint64_t)((half * 8192) >> 4), stD = stL + 2;
-                    const uint32_t d = tmem + half * 128;
-                    mma_ss(d, dK, a, IDESC_F, 0u);
-                    mma_ss(d, dK + 2, a + 2, IDESC_F, 1u);
-                    mma_ss(d, dK + 4, a + 4, IDESC_F, 1u);
-                    mma_ss(d, dK + 6, a + 6, IDESC_F, 1u);
-                    mma_ss(d, dOnes, stL, IDESC_F, 1u);               // - lse2_i / c
-                    mma_ss(d + 64, dV, bq, IDESC_F, 0u);
-                    mma_ss(d + 64, dV + 2, bq + 2, IDESC_F, 1u);
-                    mma_ss(d + 64, dV + 4, bq + 4, IDESC_F, 1u);
-                    mma_ss(d + 64, dV + 6, bq + 6, IDESC_F, 1u);
-                    mma_ss(d + 64, dOnes, stD, IDESC_F, 1u);          // - D_i
+                    const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4);
+                    const uint64_t st = stL0 + (uint64_t)((half * 8192) >> 4) + (uint64_t)(which * 2);
+                    const uint32_t d = tmem + half * 128 + which * 64;
+                    mma_ss(d, dT, a, IDESC_F, 0u);
+                    mma_ss(d, dT + 2, a + 2, IDESC_F, 1u);
+                    mma_ss(d, dT + 4, a + 4, IDESC_F, 1u);
+                    mma_ss(d, dT + 6, a + 6, IDESC_F, 1u);
+                    mma_ss(d, dOnes, st, IDESC_F, 1u);                // - lse2_i / c, or - D_i
                     tc_commit(&bars[BK1_S_FULL + half]);
                 }
             }
@@ -400,7 +400,8 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
         for (int x = 0; x < BK1_BAR_COUNT; ++x) {
             const bool many = (x >= BK1_AB_FULL && x < BK1_AB_FULL + BK1_STAGES) || (x >= BK1_P_FULL && x < BK1_P_FULL + 2) ||
                               x == BK1_WIN_FREE;
-            mbar_init(&bars[x], many ? 128u : 1u);
+            // S_FULL collects one commit from each of the two first-product issuers
+            mbar_init(&bars[x], many ? 128u : (x >= BK1_S_FULL && x < BK1_S_FULL + 2) ? 2u : 1u);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -432,8 +433,9 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        if (lane == 0 && g.total > 0) err = bk1_mma_first(P.kp, g, tmem, sK, sV, sAB, sStat, sOnes, bars, abort_flag);
+    } else if (warp == 1 || warp == 14) {
+        if (lane == 0 && g.total > 0)
+            err = bk1_mma_first(P.kp, g, warp == 1 ? 0 : 1, tmem, warp == 1 ? sK : sV, sAB, sStat, sOnes, bars, abort_flag);
         __syncwarp();
     } else if (warp < 10) {
         err = bk1_compute(P, g, (warp - 2) >> 2, tmem, bars, abort_flag);
