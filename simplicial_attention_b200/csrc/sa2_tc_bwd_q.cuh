@@ -22,7 +22,7 @@
 // sweep, so the read-modify-write needs no atomics.
 //
 // Warps (512 threads, four aligned warpgroups): 0 TMA producer, then issuer of U / W; 1 TMEM owner and
-// issuer of S / dP; 2, 3 idle; 4-7 compute (P, G); 8-11 fold (U, W into dQ / dK2 / dV2, concurrently with
+// issuer of S; 2 issuer of dP; 3 idle; 4-7 compute (P, G); 8-11 fold (U, W into dQ / dK2 / dV2, concurrently with
 // the next sweep's compute); 12-15 builders.  Every thread starts with 128 registers; the issuer
 // warpgroup releases all but 24 (setmaxnreg) and the fold and builder groups take them over.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
 // 128h+128); sweep parity p -> U [256+128p, +64), W [320+128p, +64).
@@ -160,11 +160,13 @@ __device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, ui
 // alternate between the two halves, so half == u & 1.  One thread issues about one tcgen05.mma per 90
 // cycles, so the two product stages have an issuing thread each; U / W are accumulated by one thread
 // only, which keeps the summation order fixed.
-__device__ __forceinline__ int bq_mma_first(const BqGeom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV, uint8_t *sA, uint8_t *sB,
+// which = 0: S = A_e K1^T into columns [128 half, +64) (warp 1); which = 1: dP = B_e V1^T into
+// [128 half + 64, +64) (warp 2).  A thread each: the time from "U / W of the half's previous unit are done"
+// to "the next S / dP are complete" is on the critical chain of every unit.
+__device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t tmem, uint8_t *sKV, uint8_t *sAB,
                                             uint64_t *bars, volatile int *abort_flag) {
     constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);
-    const uint64_t dK = smem_desc_sw128(smem_u32(sK)), dV = smem_desc_sw128(smem_u32(sV));
-    const uint64_t dA = smem_desc_sw128(smem_u32(sA)), dB = smem_desc_sw128(smem_u32(sB));
+    const uint64_t dT = smem_desc_sw128(smem_u32(sKV)), dA = smem_desc_sw128(smem_u32(sAB));
     if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_MMA;
     int u = 0;
     for (int e = 0; e < g.nsweeps; ++e) {
@@ -174,17 +176,12 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, uint32_t tmem, uint
             // the buffer holds P / G of this half's previous unit until its U / W products are done
             if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
             tc_fence_after();
-            const uint64_t off = (uint64_t)(((within >> 1) * TILE_BYTES + half * 8192) >> 4);
-            const uint64_t kt = dK + off, vt = dV + off;
-            const uint32_t d = tmem + half * 128;
-            mma_ss(d, dA, kt, IDESC_F, 0u);
-            mma_ss(d, dA + 2, kt + 2, IDESC_F, 1u);
-            mma_ss(d, dA + 4, kt + 4, IDESC_F, 1u);
-            mma_ss(d, dA + 6, kt + 6, IDESC_F, 1u);
-            mma_ss(d + 64, dB, vt, IDESC_F, 0u);
-            mma_ss(d + 64, dB + 2, vt + 2, IDESC_F, 1u);
-            mma_ss(d + 64, dB + 4, vt + 4, IDESC_F, 1u);
-            mma_ss(d + 64, dB + 6, vt + 6, IDESC_F, 1u);
+            const uint64_t t = dT + (uint64_t)(((within >> 1) * TILE_BYTES + half * 8192) >> 4);
+            const uint32_t d = tmem + half * 128 + which * 64;
+            mma_ss(d, dA, t, IDESC_F, 0u);
+            mma_ss(d, dA + 2, t + 2, IDESC_F, 1u);
+            mma_ss(d, dA + 4, t + 4, IDESC_F, 1u);
+            mma_ss(d, dA + 6, t + 6, IDESC_F, 1u);
             tc_commit(&bars[BQ_S_FULL + half]);
         }
         tc_commit(&bars[BQ_AB_EMPTY]);
@@ -440,7 +437,9 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     if (threadIdx.x == 0) {
         for (int x = 0; x < BQ_BAR_COUNT; ++x) {
             const bool many = x == BQ_AB_FULL || (x >= BQ_P_FULL && x < BQ_P_FULL + 2) || (x >= BQ_W_EMPTY && x < BQ_W_EMPTY + 2);
-            mbar_init(&bars[x], many ? 128u : 1u);
+            // S_FULL and AB_EMPTY collect one commit from each of the two first-product issuers
+            const bool two = (x >= BQ_S_FULL && x < BQ_S_FULL + 2) || x == BQ_AB_EMPTY;
+            mbar_init(&bars[x], many ? 128u : two ? 2u : 1u);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -473,8 +472,9 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
                 else err = bq_mma_second(g, tmem, sK, sV, bars, abort_flag);
             }
             __syncwarp();
-        } else if (warp == 1) {
-            if (lane == 0 && g.total > 0) err = bq_mma_first(g, tmem, sK, sV, sA, sB, bars, abort_flag);
+        } else if (warp == 1 || warp == 2) {
+            if (lane == 0 && g.total > 0)
+                err = bq_mma_first(g, warp - 1, tmem, warp == 1 ? sK : sV, warp == 1 ? sA : sB, bars, abort_flag);
             __syncwarp();
         }
     } else if (warp < 8) {
