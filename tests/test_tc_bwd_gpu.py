@@ -37,6 +37,8 @@ CASES = [
     (1, 640, 2, 2, 512, 32),
     (1, 520, 1, 1, 700, 3),       # w1 beyond the forward's resident window: forward falls back, backward does not
     (1, 400, 2, 2, 1, 1),
+    (1, 300, 2, 1, 200, 40),      # w2 above 32: second-key rows are read from global memory, not staged
+    (1, 640, 1, 1, 512, 64),      # w2 above the dQ/dK2/dV2 kernel's shared accumulators: that part runs in fp32
 ]
 
 
