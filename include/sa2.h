@@ -173,6 +173,41 @@ const char *sa2_strerror(int status);
 /* Library version as major*10000 + minor*100 + patch. */
 int sa2_version(void);
 
+/*
+ * Per-head RMSNorm of a packed projection - stands in for the five RMSNorm
+ * modules the reference applies to q, k, k', v, v' after splitting its fused
+ * projection (simplicial_attention/simplicial_mha.py:69-73,124-127).
+ *
+ * x is [rows][channels] with row stride x_stride (elements), channels
+ * contiguous; every group of d consecutive channels is one head; weight holds
+ * one gain per channel (each norm's d gains tiled over its heads):
+ *   rstd[r][g] = rsqrt(mean_{c in head g} x[r][c]^2 + eps)
+ *   y[r][c]    = x[r][c] * rstd[r][c / d] * weight[c]
+ * sa2_headnorm_bwd returns dx (layout and dtype of x) and dweight[channels];
+ * `partial` is caller-owned scratch of sa2_headnorm_partial_bytes().  d must be
+ * 32, 64 or 128 and channels a multiple of d.  x_dtype / y_dtype are the
+ * element types of x (and dx) and of y (and dy).
+ */
+typedef struct sa2_headnorm_args {
+    const void *x;
+    const void *dy;        /* backward only */
+    const float *weight;
+    void *y;               /* forward: y; backward: dx */
+    float *rstd;           /* [rows][channels / d]: written by the forward, read by the backward */
+    float *dweight;        /* backward only: [channels] */
+    void *partial;         /* backward only */
+    size_t partial_bytes;
+    int64_t rows, x_stride, y_stride, dy_stride;
+    int32_t channels, d;
+    int32_t x_dtype, y_dtype;
+    float eps;
+    void *stream;
+} sa2_headnorm_args;
+
+int sa2_headnorm_fwd(const sa2_headnorm_args *args);
+int sa2_headnorm_bwd(const sa2_headnorm_args *args);
+size_t sa2_headnorm_partial_bytes(int64_t rows, int32_t channels);
+
 #ifdef __cplusplus
 }
 #endif

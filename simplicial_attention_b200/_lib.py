@@ -17,7 +17,8 @@ KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "tcgen05": KERNEL_TCGEN05}
 
 # symbols declared in include/sa2.h
 EXPORTS = ("sa2_fwd", "sa2_bwd", "sa2_bwd_workspace_bytes", "sa2_strerror", "sa2_version",
-           "sa2_kernel_launches", "sa2_device_status", "sa2_bwd_static_scratch")
+           "sa2_kernel_launches", "sa2_device_status", "sa2_bwd_static_scratch",
+           "sa2_headnorm_fwd", "sa2_headnorm_bwd", "sa2_headnorm_partial_bytes")
 STATIC_SCRATCH_ROWS = 262144   # SA2_STATIC_SCRATCH_ROWS in include/sa2.h
 
 
@@ -58,6 +59,16 @@ class BwdArgs(C.Structure):
     ]
 
 
+class HeadnormArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("dy", C.c_void_p), ("weight", C.c_void_p), ("y", C.c_void_p), ("rstd", C.c_void_p),
+        ("dweight", C.c_void_p), ("partial", C.c_void_p), ("partial_bytes", C.c_size_t),
+        ("rows", C.c_int64), ("x_stride", C.c_int64), ("y_stride", C.c_int64), ("dy_stride", C.c_int64),
+        ("channels", C.c_int32), ("d", C.c_int32), ("x_dtype", C.c_int32), ("y_dtype", C.c_int32),
+        ("eps", C.c_float), ("stream", C.c_void_p),
+    ]
+
+
 _lock = threading.Lock()
 _lib = None
 
@@ -93,6 +104,12 @@ def lib() -> C.CDLL:
         handle.sa2_device_status.restype = C.c_int
         handle.sa2_strerror.argtypes = [C.c_int]
         handle.sa2_strerror.restype = C.c_char_p
+        handle.sa2_headnorm_fwd.argtypes = [C.POINTER(HeadnormArgs)]
+        handle.sa2_headnorm_fwd.restype = C.c_int
+        handle.sa2_headnorm_bwd.argtypes = [C.POINTER(HeadnormArgs)]
+        handle.sa2_headnorm_bwd.restype = C.c_int
+        handle.sa2_headnorm_partial_bytes.argtypes = [C.c_int64, C.c_int32]
+        handle.sa2_headnorm_partial_bytes.restype = C.c_size_t
         handle.sa2_version.argtypes = []
         handle.sa2_version.restype = C.c_int
         _lib = handle

@@ -4,6 +4,7 @@
 #include "sa2_common.cuh"
 #include "sa2_simt.cuh"
 #include "sa2_tc.cuh"
+#include "sa2_headnorm.cuh"
 
 namespace {
 
@@ -271,5 +272,83 @@ int sa2_bwd_static_scratch(const sa2_bwd_args *a) {
         default: return simt_bwd<128>(p, st);
     }
 }
+
+}  // extern "C"
+
+// ---------------------------------------------------------------- per-head RMSNorm
+namespace {
+
+int headnorm_grid(int64_t rows) {
+    const int64_t want = (rows + sa2::headnorm::WARPS - 1) / sa2::headnorm::WARPS;
+    return (int)(want < 592 ? (want > 0 ? want : 1) : 592);          // 4 CTAs per SM
+}
+
+int headnorm_check(const sa2_headnorm_args *a, bool backward) {
+    if (!a || !a->x || !a->weight || !a->y || !a->rstd || a->rows <= 0 || a->channels <= 0) return SA2_ERR_INVALID;
+    if (a->d != 32 && a->d != 64 && a->d != 128) return SA2_ERR_UNSUPPORTED;
+    if (a->channels % a->d != 0) return SA2_ERR_INVALID;
+    if ((a->x_dtype != SA2_F32 && a->x_dtype != SA2_BF16) || (a->y_dtype != SA2_F32 && a->y_dtype != SA2_BF16)) return SA2_ERR_UNSUPPORTED;
+    if (a->x_stride < a->channels || a->y_stride < a->channels) return SA2_ERR_INVALID;
+    if (backward) {
+        if (!a->dy || !a->dweight || a->dy_stride < a->channels) return SA2_ERR_INVALID;
+        if (!a->partial || a->partial_bytes < sa2_headnorm_partial_bytes(a->rows, a->channels)) return SA2_ERR_WORKSPACE;
+    }
+    return SA2_OK;
+}
+
+template <typename TX, typename TY>
+int headnorm_launch(const sa2_headnorm_args *a, const sa2::headnorm::Params &P, bool backward) {
+    using namespace sa2::headnorm;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
+    if (!backward) {
+        const int64_t pairs = a->rows * (a->channels / a->d);
+        const int grid = (int)((pairs + WARPS - 1) / WARPS < 148 * 16 ? (pairs + WARPS - 1) / WARPS : 148 * 16);
+        if (a->d == 32) fwd_kernel<TX, TY, 1><<<grid, WARPS * 32, 0, st>>>(P);
+        else if (a->d == 64) fwd_kernel<TX, TY, 2><<<grid, WARPS * 32, 0, st>>>(P);
+        else fwd_kernel<TX, TY, 4><<<grid, WARPS * 32, 0, st>>>(P);
+    } else {
+        const int grid = headnorm_grid(a->rows);
+        const size_t smem = (size_t)WARPS * a->channels * sizeof(float);
+        auto run = [&](auto kern) -> int {
+            if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return SA2_ERR_CUDA;
+            kern<<<grid, WARPS * 32, smem, st>>>(P);
+            return SA2_OK;
+        };
+        int rc;
+        if (a->d == 32) rc = run(bwd_kernel<TX, TY, 1>);
+        else if (a->d == 64) rc = run(bwd_kernel<TX, TY, 2>);
+        else rc = run(bwd_kernel<TX, TY, 4>);
+        if (rc != SA2_OK) return rc;
+        dweight_reduce_kernel<<<(a->channels + 255) / 256, 256, 0, st>>>(P.partial, a->dweight, grid, a->channels);
+    }
+    return cudaGetLastError() == cudaSuccess ? SA2_OK : SA2_ERR_CUDA;
+}
+
+int headnorm_dispatch(const sa2_headnorm_args *a, bool backward) {
+    const int rc = headnorm_check(a, backward);
+    if (rc != SA2_OK) return rc;
+    if ((size_t)sa2::headnorm::WARPS * a->channels * sizeof(float) > 200 * 1024) return SA2_ERR_UNSUPPORTED;
+    sa2::headnorm::Params P;
+    P.x = a->x; P.dy = a->dy; P.weight = a->weight; P.y = a->y; P.rstd = a->rstd;
+    P.partial = reinterpret_cast<float *>(a->partial);
+    P.rows = a->rows; P.x_stride = a->x_stride; P.y_stride = a->y_stride; P.dy_stride = a->dy_stride;
+    P.channels = a->channels; P.d = a->d; P.eps = a->eps;
+    const bool xb = a->x_dtype == SA2_BF16, yb = a->y_dtype == SA2_BF16;
+    if (xb && yb) return headnorm_launch<__nv_bfloat16, __nv_bfloat16>(a, P, backward);
+    if (xb) return headnorm_launch<__nv_bfloat16, float>(a, P, backward);
+    if (yb) return headnorm_launch<float, __nv_bfloat16>(a, P, backward);
+    return headnorm_launch<float, float>(a, P, backward);
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t sa2_headnorm_partial_bytes(int64_t rows, int32_t channels) {
+    if (rows <= 0 || channels <= 0) return 0;
+    return (size_t)headnorm_grid(rows) * (size_t)channels * sizeof(float);
+}
+int sa2_headnorm_fwd(const sa2_headnorm_args *a) { return headnorm_dispatch(a, false); }
+int sa2_headnorm_bwd(const sa2_headnorm_args *a) { return headnorm_dispatch(a, true); }
 
 }  // extern "C"

@@ -87,10 +87,40 @@ class HigherOrderAttention(Module):
         t = t.view(b, n, heads, -1)
         return t.transpose(1, 2) if self.head_first_dim else t
 
+    # One kernel normalises the whole fused projection instead of five RMSNorm modules plus casts
+    # (CUDA tensors only; set to False to run the norms as separate torch modules, as the reference does).
+    fused_head_norm = True
+
+    def _fused_norm(self, proj):
+        """Per-head RMSNorm of the packed projection with the gains of q_norm / k_norms / v_norms tiled to
+        one entry per channel; same arithmetic as the modules, applied before the split."""
+        import torch
+
+        from .headnorm import head_rmsnorm
+        kw = torch.cat([n.weight for n in self.k_norms]).repeat(self.key_value_heads)
+        vw = torch.cat([n.weight for n in self.v_norms]).repeat(self.key_value_heads)
+        weight = torch.cat((self.q_norm.weight.repeat(self.heads), kw, vw))
+        autocast = torch.is_autocast_enabled()
+        # the modules leave eps unset: the machine epsilon of the dtype they compute in (fp32 under autocast)
+        eps = self.q_norm.eps if self.q_norm.eps is not None else \
+            torch.finfo(torch.float32 if autocast else proj.dtype).eps
+        out_dtype = torch.get_autocast_dtype("cuda") if autocast else proj.dtype
+        return head_rmsnorm(proj, weight, self.dim_head, eps, out_dtype)
+
     def _project(self, tokens):
         """tokens -> (queries, keys, values) after the head split and the per-head norms."""
         tokens = self.prenorm(tokens)
-        q, k, v = self.to_qkv(tokens).split(self.split_dims, dim=-1)
+        proj = self.to_qkv(tokens)
+        fused = (self.fused_head_norm and self.qk_rmsnorm and proj.is_cuda and not self.head_first_dim
+                 and self.dim_head_values == self.dim_head and self.dim_head in (32, 64, 128)
+                 and proj.dtype in (torch.float32, torch.bfloat16))
+        if fused:
+            q, k, v = self._fused_norm(proj).split(self.split_dims, dim=-1)
+            queries = self._split(q, self.heads)
+            keys = self._split(k, self.key_value_heads).chunk(self.kv_sets, dim=-1)
+            values = self._split(v, self.key_value_heads).chunk(self.kv_sets, dim=-1)
+            return queries, keys, values
+        q, k, v = proj.split(self.split_dims, dim=-1)
 
         queries = self._split(q, self.heads)
         # each kv head's slice holds its key sets side by side: [k1 | k2]
