@@ -185,7 +185,8 @@ int sa2_version(void);
  *   y[r][c]    = x[r][c] * rstd[r][c / d] * weight[c]
  * sa2_headnorm_bwd returns dx (layout and dtype of x) and dweight[channels];
  * `partial` is caller-owned scratch of sa2_headnorm_partial_bytes().  d must be
- * 32, 64 or 128 and channels a multiple of d.  x_dtype / y_dtype are the
+ * 32, 64, 128, 256 or 512 (with channels = d it is an ordinary RMSNorm over the
+ * whole row) and channels a multiple of d.  x_dtype / y_dtype are the
  * element types of x (and dx) and of y (and dy).
  */
 typedef struct sa2_headnorm_args {

@@ -285,7 +285,7 @@ int headnorm_grid(int64_t rows) {
 
 int headnorm_check(const sa2_headnorm_args *a, bool backward) {
     if (!a || !a->x || !a->weight || !a->y || !a->rstd || a->rows <= 0 || a->channels <= 0) return SA2_ERR_INVALID;
-    if (a->d != 32 && a->d != 64 && a->d != 128) return SA2_ERR_UNSUPPORTED;
+    if (a->d != 32 && a->d != 64 && a->d != 128 && a->d != 256 && a->d != 512) return SA2_ERR_UNSUPPORTED;
     if (a->channels % a->d != 0) return SA2_ERR_INVALID;
     if ((a->x_dtype != SA2_F32 && a->x_dtype != SA2_BF16) || (a->y_dtype != SA2_F32 && a->y_dtype != SA2_BF16)) return SA2_ERR_UNSUPPORTED;
     if (a->x_stride < a->channels || a->y_stride < a->channels) return SA2_ERR_INVALID;
@@ -305,7 +305,9 @@ int headnorm_launch(const sa2_headnorm_args *a, const sa2::headnorm::Params &P, 
         const int grid = (int)((pairs + WARPS - 1) / WARPS < 148 * 16 ? (pairs + WARPS - 1) / WARPS : 148 * 16);
         if (a->d == 32) fwd_kernel<TX, TY, 1><<<grid, WARPS * 32, 0, st>>>(P);
         else if (a->d == 64) fwd_kernel<TX, TY, 2><<<grid, WARPS * 32, 0, st>>>(P);
-        else fwd_kernel<TX, TY, 4><<<grid, WARPS * 32, 0, st>>>(P);
+        else if (a->d == 128) fwd_kernel<TX, TY, 4><<<grid, WARPS * 32, 0, st>>>(P);
+        else if (a->d == 256) fwd_kernel<TX, TY, 8><<<grid, WARPS * 32, 0, st>>>(P);
+        else fwd_kernel<TX, TY, 16><<<grid, WARPS * 32, 0, st>>>(P);
     } else {
         const int grid = headnorm_grid(a->rows);
         const size_t smem = (size_t)WARPS * a->channels * sizeof(float);
@@ -317,7 +319,9 @@ int headnorm_launch(const sa2_headnorm_args *a, const sa2::headnorm::Params &P, 
         int rc;
         if (a->d == 32) rc = run(bwd_kernel<TX, TY, 1>);
         else if (a->d == 64) rc = run(bwd_kernel<TX, TY, 2>);
-        else rc = run(bwd_kernel<TX, TY, 4>);
+        else if (a->d == 128) rc = run(bwd_kernel<TX, TY, 4>);
+        else if (a->d == 256) rc = run(bwd_kernel<TX, TY, 8>);
+        else rc = run(bwd_kernel<TX, TY, 16>);
         if (rc != SA2_OK) return rc;
         dweight_reduce_kernel<<<(a->channels + 255) / 256, 256, 0, st>>>(P.partial, a->dweight, grid, a->channels);
     }

@@ -36,6 +36,10 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// channel of a lane's k-th element within its head: a few contiguous elements per lane for narrow heads (one
+// 4- or 8-byte access), interleaved by warp for wide ones (every access of the warp is one contiguous run)
+template <int PER> __device__ __forceinline__ int chan(int lane, int k) { return PER <= 4 ? lane * PER + k : k * 32 + lane; }
+
 struct Params {
     const void *x;        // [rows][x_stride], channels contiguous
     const void *dy;       // backward only: [rows][dy_stride]
@@ -44,7 +48,7 @@ struct Params {
     float *rstd;          // [rows][groups]
     float *partial;       // backward: [gridDim.x][channels]
     int64_t rows, x_stride, y_stride, dy_stride;
-    int channels, d;      // d in {32, 64, 128}: d / 32 elements per lane
+    int channels, d;      // d in {32, 64, 128, 256, 512}: d / 32 elements per lane
     float eps;
 };
 
@@ -58,13 +62,16 @@ __global__ void __launch_bounds__(WARPS * 32) fwd_kernel(const Params P) {
     TY *y = reinterpret_cast<TY *>(P.y);
     for (int64_t p = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5); p < pairs; p += (int64_t)gridDim.x * WARPS) {
         const int64_t r = p / groups;
-        const int c0 = (int)(p % groups) * P.d + lane * PER;
+        const int c0 = (int)(p % groups) * P.d;
         float v[PER], ss = 0.f;
 #pragma unroll
-        for (int k = 0; k < PER; ++k) { v[k] = to_f<TX>(x[r * P.x_stride + c0 + k]); ss += v[k] * v[k]; }
+        for (int k = 0; k < PER; ++k) { v[k] = to_f<TX>(x[r * P.x_stride + c0 + chan<PER>(lane, k)]); ss += v[k] * v[k]; }
         const float rs = rsqrtf(warp_sum(ss) / (float)P.d + P.eps);
 #pragma unroll
-        for (int k = 0; k < PER; ++k) y[r * P.y_stride + c0 + k] = from_f<TY>(v[k] * rs * P.weight[c0 + k]);
+        for (int k = 0; k < PER; ++k) {
+            const int c = c0 + chan<PER>(lane, k);
+            y[r * P.y_stride + c] = from_f<TY>(v[k] * rs * P.weight[c]);
+        }
         if (lane == 0) P.rstd[p] = rs;
     }
 }
@@ -86,20 +93,21 @@ __global__ void __launch_bounds__(WARPS * 32) bwd_kernel(const Params P) {
     float *mine = acc + (size_t)warp * P.channels;
     for (int64_t r = r_begin + warp; r < r_end; r += WARPS) {
         for (int g = 0; g < groups; ++g) {
-            const int c0 = g * P.d + lane * PER;
+            const int c0 = g * P.d;
             const float rs = P.rstd[r * groups + g];
             float xh[PER], gy[PER], dot = 0.f;
 #pragma unroll
             for (int k = 0; k < PER; ++k) {
-                xh[k] = to_f<TX>(x[r * P.x_stride + c0 + k]) * rs;
-                const float d_ = to_f<TY>(dy[r * P.dy_stride + c0 + k]);
-                gy[k] = d_ * P.weight[c0 + k];
+                const int c = c0 + chan<PER>(lane, k);
+                xh[k] = to_f<TX>(x[r * P.x_stride + c]) * rs;
+                const float d_ = to_f<TY>(dy[r * P.dy_stride + c]);
+                gy[k] = d_ * P.weight[c];
                 dot += gy[k] * xh[k];
-                mine[c0 + k] += d_ * xh[k];
+                mine[c] += d_ * xh[k];
             }
             const float m = warp_sum(dot) / (float)P.d;
 #pragma unroll
-            for (int k = 0; k < PER; ++k) dx[r * P.y_stride + c0 + k] = from_f<TX>(rs * (gy[k] - xh[k] * m));
+            for (int k = 0; k < PER; ++k) dx[r * P.y_stride + c0 + chan<PER>(lane, k)] = from_f<TX>(rs * (gy[k] - xh[k] * m));
         }
     }
     __syncthreads();

@@ -68,3 +68,25 @@ def head_rmsnorm(x, weight, d, eps, out_dtype=None):
     """``y[..., c] = x[..., c] * rsqrt(mean over c's head of x^2 + eps) * weight[c]``; ``weight`` has one
     entry per channel.  ``out_dtype`` defaults to ``x.dtype``."""
     return HeadRMSNorm.apply(x, weight, int(d), float(eps), x.dtype if out_dtype is None else out_dtype)
+
+
+class RMSNorm(torch.nn.Module):
+    """``torch.nn.RMSNorm(dim)`` with the same parameter (``weight``) and arithmetic, run by the fused kernel
+    on CUDA when ``dim`` is 32 ... 512 (a power of two times 32); under autocast the result is produced in
+    the autocast dtype directly - its consumers here are linear layers, which would round it anyway."""
+
+    def __init__(self, dim, eps=None):
+        super().__init__()
+        self.dim, self.eps = dim, eps
+        self.weight = torch.nn.Parameter(torch.ones(dim))
+
+    def forward(self, x):
+        fused = x.is_cuda and self.dim in (32, 64, 128, 256, 512) and x.dtype in _DTYPES
+        if not fused:
+            return torch.nn.functional.rms_norm(x, (self.dim,), self.weight, self.eps)
+        autocast = torch.is_autocast_enabled()
+        eps = self.eps if self.eps is not None else torch.finfo(torch.float32 if autocast else x.dtype).eps
+        out_dtype = torch.get_autocast_dtype("cuda") if autocast else x.dtype
+        if out_dtype not in _DTYPES:
+            out_dtype = x.dtype
+        return head_rmsnorm(x, self.weight, self.dim, eps, out_dtype)

@@ -19,6 +19,7 @@ import torch
 from torch.nn import Identity, Linear, Module, ModuleList, RMSNorm
 
 from .attention import divisible_by, exists, sliding_two_simplicial_attn
+from .headnorm import RMSNorm as RowRMSNorm
 
 
 def default(v, d):
@@ -60,8 +61,9 @@ class HigherOrderAttention(Module):
         self.kv_sets = number_key_value_sets
         self.head_first_dim = head_first_dim
 
-        self.prenorm = RMSNorm(dim) if prenorm else Identity()
-        self.postnorm = RMSNorm(dim) if postnorm else Identity()
+        # same parameter as torch.nn.RMSNorm; one fused kernel on CUDA
+        self.prenorm = RowRMSNorm(dim) if prenorm else Identity()
+        self.postnorm = RowRMSNorm(dim) if postnorm else Identity()
 
         self.qk_rmsnorm = qk_rmsnorm
         if qk_rmsnorm:

@@ -8,7 +8,8 @@ the ``TwoSimplicialLM`` wrapper of the reference's example script
 (train.py:64-135; the script itself runs its training loop at import and needs
 a dataset blob that is not shipped).  Parameter names match the reference, so
 its checkpoints load.  Only the simplicial layers run our kernels; the standard
-layers use torch's scaled-dot-product attention, as in the reference.
+layers use torch's scaled-dot-product attention, as in the reference; the RMSNorm modules are
+``headnorm.RMSNorm`` (same parameter, fused CUDA kernel).
 """
 from __future__ import annotations
 
@@ -20,6 +21,7 @@ from torch import nn
 from torch.nn import Module, ModuleList
 
 from .attention import divisible_by
+from .headnorm import RMSNorm
 from .mha import SlidingWindowTwoSimplicialMHA
 
 
@@ -30,7 +32,7 @@ class Attention(Module):
         super().__init__()
         assert divisible_by(heads, key_value_heads)
         self.heads, self.key_value_heads, self.dim_head = heads, key_value_heads, dim_head
-        self.prenorm = nn.RMSNorm(dim)
+        self.prenorm = RMSNorm(dim)
         self.to_q = nn.Linear(dim, heads * dim_head, bias=False)
         self.to_kv = nn.Linear(dim, key_value_heads * dim_head * 2, bias=False)
         self.to_out = nn.Linear(heads * dim_head, dim, bias=False)
@@ -53,7 +55,7 @@ class Attention(Module):
 
 def FeedForward(dim, expansion=4.0):
     inner = int(dim * expansion)
-    return nn.Sequential(nn.RMSNorm(dim), nn.Linear(dim, inner), nn.GELU(), nn.Linear(inner, dim))
+    return nn.Sequential(RMSNorm(dim), nn.Linear(dim, inner), nn.GELU(), nn.Linear(inner, dim))
 
 
 class TwoSimplicialTransformer(Module):
@@ -70,7 +72,7 @@ class TwoSimplicialTransformer(Module):
                 attn = Attention(dim=dim, heads=heads, key_value_heads=key_value_heads, dim_head=dim_head, **attn_kwargs)
             layers.append(ModuleList([attn, FeedForward(dim=dim, expansion=ff_expansion)]))
         self.layers = ModuleList(layers)
-        self.norm = nn.RMSNorm(dim) if final_norm else nn.Identity()
+        self.norm = RMSNorm(dim) if final_norm else nn.Identity()
 
     def forward(self, x, cache=None, return_cache=False):
         """``cache``: one entry per layer, as returned by an earlier call with ``return_cache=True``."""

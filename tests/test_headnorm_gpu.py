@@ -71,3 +71,32 @@ def test_bitwise_repeatable():
         head_rmsnorm(x, gain, 64, 1e-6).backward(dy)
         res.append((x.grad.clone(), gain.grad.clone()))
     assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+
+
+@pytest.mark.parametrize("dim", [256, 512])
+def test_row_rmsnorm_module_matches_torch(dim):
+    from simplicial_attention_b200.headnorm import RMSNorm
+
+    torch.manual_seed(2)
+    ours, ref = RMSNorm(dim).cuda(), torch.nn.RMSNorm(dim).cuda()
+    with torch.no_grad():
+        ours.weight.add_(0.1 * torch.randn(dim, device="cuda"))
+        ref.weight.copy_(ours.weight)
+    x = torch.randn(4, 333, dim, device="cuda")
+    dy = torch.randn_like(x)
+    res = []
+    for m in (ours, ref):
+        xi = x.clone().requires_grad_()
+        m(xi).backward(dy)
+        res.append((m(xi).detach(), xi.grad, m.weight.grad.clone()))
+        m.weight.grad = None
+    for a, b in zip(*res):
+        assert (a - b).abs().max().item() <= 1e-5 * max(1.0, b.abs().max().item())
+    # under autocast: bf16 out, fp32 gradients for the fp32 input
+    xi = x.clone().requires_grad_()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = ours(xi)
+    assert y.dtype == torch.bfloat16
+    y.backward(dy.to(torch.bfloat16))
+    assert xi.grad.dtype == torch.float32
+    assert (y.float() - res[1][0]).abs().max().item() <= 2e-2 * res[1][0].abs().max().item()
