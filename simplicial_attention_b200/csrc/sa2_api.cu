@@ -323,7 +323,7 @@ int headnorm_launch(const sa2_headnorm_args *a, const sa2::headnorm::Params &P, 
         else if (a->d == 256) rc = run(bwd_kernel<TX, TY, 8>);
         else rc = run(bwd_kernel<TX, TY, 16>);
         if (rc != SA2_OK) return rc;
-        dweight_reduce_kernel<<<(a->channels + 255) / 256, 256, 0, st>>>(P.partial, a->dweight, grid, a->channels);
+        dweight_reduce_kernel<<<(a->channels + 31) / 32, 256, 0, st>>>(P.partial, a->dweight, grid, a->channels);
     }
     return cudaGetLastError() == cudaSuccess ? SA2_OK : SA2_ERR_CUDA;
 }

@@ -13,7 +13,7 @@
 // One warp per (row, head): HBM-bound, every element is read once and written
 // once.  dweight is reduced without atomics: each CTA sums its rows in shared
 // memory in warp order and writes one partial row; a second kernel adds the
-// partial rows in a fixed order.
+// partial rows in a fixed order (eight interleaved slices, then the slices).
 #pragma once
 #include "sa2_common.cuh"
 #include <cuda_bf16.h>
@@ -119,12 +119,23 @@ __global__ void __launch_bounds__(WARPS * 32) bwd_kernel(const Params P) {
     }
 }
 
-__global__ void dweight_reduce_kernel(const float *partial, float *dweight, int nparts, int channels) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= channels) return;
+// 32 channels x 8 slices per CTA: slice j adds partial rows j, j + 8, ... in order, then the eight slice sums
+// are added in order - a fixed summation tree, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) dweight_reduce_kernel(const float *partial, float *dweight, int nparts, int channels) {
+    __shared__ float part[8][32];
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
     float s = 0.f;
-    for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * channels + c];
-    dweight[c] = s;
+    if (c < channels)
+        for (int p = slice; p < nparts; p += 8) s += partial[(size_t)p * channels + c];
+    part[slice][lane] = s;
+    __syncthreads();
+    if (slice == 0 && c < channels) {
+        float t = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t += part[j][lane];
+        dweight[c] = t;
+    }
 }
 
 }  // namespace headnorm
