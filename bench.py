@@ -75,15 +75,55 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML read-only queries from a
+    thread every few milliseconds (the timed region of the default run lasts ~55 ms, less than nvidia-smi
+    needs to start), nvidia-smi as the fallback."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.nvml, self.stop_flag = index, [], None, None, False
+
+    def _nvml_loop(self):
+        n, h = self.nvml
+        masks = (n.nvmlClocksEventReasonHwSlowdown if hasattr(n, "nvmlClocksEventReasonHwSlowdown") else 0x8,
+                 n.nvmlClocksEventReasonHwThermalSlowdown if hasattr(n, "nvmlClocksEventReasonHwThermalSlowdown") else 0x40,
+                 n.nvmlClocksEventReasonSwThermalSlowdown if hasattr(n, "nvmlClocksEventReasonSwThermalSlowdown") else 0x20,
+                 n.nvmlClocksEventReasonSwPowerCap if hasattr(n, "nvmlClocksEventReasonSwPowerCap") else 0x4)
+        query = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+        while not self.stop_flag:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
+                bits = query(h)
+                self.rows.append([str(sm), str(mx)] + ["Active" if bits & m else "Not Active" for m in masks])
+            except Exception:
+                break
+            time.sleep(0.004)
 
     def start(self):
+        try:
+            import pynvml as n
+            n.nvmlInit()
+            # the process may see a subset of the machine's GPUs: map the CUDA index through its UUID
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            handle = None
+            for k in range(n.nvmlDeviceGetCount()):
+                h = n.nvmlDeviceGetHandleByIndex(k)
+                u = n.nvmlDeviceGetUUID(h)
+                u = u.decode() if isinstance(u, bytes) else u
+                if uuid in u:
+                    handle = h
+            if handle is None:
+                handle = n.nvmlDeviceGetHandleByIndex(self.index)
+            self.nvml = (n, handle)
+            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -98,22 +138,25 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
-        if not self.proc:
+        if self.nvml:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+        elif self.proc:
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+        else:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        self.thread.join(timeout=2)
         sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for r in self.rows:
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
             except (ValueError, IndexError):
                 continue
-            for name, val in zip(names, r[2:6]):
+            for name, val in zip(self.NAMES, r[2:6]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "source": "nvml" if self.nvml else "nvidia-smi", "reasons": sorted(reasons)}
 
 
 def make_inputs(cfg, seed, dtype, device, pin=False):
