@@ -71,3 +71,27 @@ def test_workspace_size():
     need = lib.sa2_bwd_workspace_bytes(C.byref(s))
     assert need >= 2 * 4 * 100 * 4 and need % 256 == 0
     assert lib.sa2_bwd_workspace_bytes(C.byref(_shape(d=48))) == 0
+
+
+def test_headnorm_argument_errors():
+    lib = _lib.lib()
+    assert lib.sa2_headnorm_fwd(None) == 1 and lib.sa2_headnorm_bwd(None) == 1
+    a = _lib.HeadnormArgs()
+    assert lib.sa2_headnorm_fwd(C.byref(a)) == 1                     # null pointers
+    # fake (never dereferenced) addresses: validation happens before any launch
+    a.x, a.weight, a.y, a.rstd = 256, 256, 256, 256
+    a.rows, a.channels, a.x_stride, a.y_stride = 8, 96, 96, 96
+    a.d = 48
+    assert lib.sa2_headnorm_fwd(C.byref(a)) == 2                     # group width not supported
+    a.d, a.channels = 64, 96
+    assert lib.sa2_headnorm_fwd(C.byref(a)) == 1                     # channels not a multiple of d
+    a.channels, a.x_stride, a.y_stride = 128, 128, 100
+    assert lib.sa2_headnorm_fwd(C.byref(a)) == 1                     # row stride shorter than a row
+    a.y_stride, a.x_dtype = 128, 9
+    assert lib.sa2_headnorm_fwd(C.byref(a)) == 2                     # unknown dtype
+    a.x_dtype = 0
+    a.dy, a.dweight, a.dy_stride = 256, 256, 128
+    assert lib.sa2_headnorm_bwd(C.byref(a)) == 3                     # scratch missing
+    assert lib.sa2_headnorm_partial_bytes(8, 128) == 1 * 128 * 4
+    assert lib.sa2_headnorm_partial_bytes(10 ** 6, 1536) == 592 * 1536 * 4
+    assert lib.sa2_headnorm_partial_bytes(0, 128) == 0
