@@ -1,6 +1,6 @@
 """Benchmark of sliding-window causal 2-simplicial attention, forward + backward.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C3|C2|C5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload C3|C2|C5|C4]
                     [--kernel auto|simt|tcgen05] [--impl ours|reference]
 
 A step is one forward + backward pass of the operator over one batch of
@@ -19,8 +19,12 @@ Prints ONE JSON line:
             q, k, k', v, v', dO and device->host copy of out and the five
             gradients inside the timed region, overlapped with the kernels by
             batch chunks (sequence sharding: the autograd API, serial copies);
-  roofline  the dominant phase (the backward entry point) against the measured
-            dense bf16 tensor peak of this pool's B200s;
+  roofline  the dominant kernel (timed alone, live, with CUDA events) against the
+            measured burst bf16 tensor peak of this pool's B200s, the sustained
+            figure beside it; `kernels` lists all three tensor-core kernels;
+  seq       (N > 1) the same tensors as ONE sequence of length n*N in sequence
+            blocks with the NCCL halo exchange; c5: the long-sequence
+            configuration (b8 h16 n16384 d128) split over the N ranks;
   cpu_baseline  the CPU oracle timed on this machine's host cores on a bounded
             sample of the same workload (rank 0, N=1 only).
 
@@ -62,16 +66,6 @@ def valid_pairs(n, w1, w2):
 def work_flops(cfg):
     p = valid_pairs(cfg["n"], cfg["w1"], cfg["w2"]) * cfg["b"] * cfg["hq"]
     return {"fwd": 4 * cfg["d"] * p, "bwd": 10 * cfg["d"] * p, "fwd_bwd": 14 * cfg["d"] * p}
-
-
-def measured_peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            m = json.load(f)
-        return {"tflops": float(m.get("bf16_tflops_sustained") or m["bf16_tflops"]), "hbm_gbs": float(m["hbm_gbs"]),
-                "source": "measured (MEASURED_PEAKS.json, sustained cuBLAS bf16)"}
-    return {"tflops": 1400.0, "hbm_gbs": 6650.0, "source": "fallback (earlier measurement on this pool, sustained)"}
 
 
 class ClockSampler:
@@ -185,12 +179,36 @@ def barrier(world):
     torch.cuda.synchronize()
 
 
-def cpu_oracle_sample(cfg, steps=1, warmup=0):
-    """Oracle forward + backward on the bounded CPU sample; returns (TFLOP/s, seconds per pass, description)."""
+def host_threads():
+    """Host threads this process may use.  A launcher such as torch.distributed.run exports
+    OMP_NUM_THREADS=1; the CPU arm uses every core its affinity mask allows instead."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
+def cpu_oracle_sample(cfg, steps=1, warmup=0, budget_s=None):
+    """Oracle forward + backward on a bounded CPU sample; returns (TFLOP/s, seconds per pass, description,
+    sample).  With ``budget_s`` the sample ((batch, head) pairs of up to 4096 rows) is sized from a one-pair
+    probe so that warmup + steps passes fit the budget."""
     from oracle import oracle as O
     s = dict(cfg)
     s.update(CPU_SAMPLE)
     s["n"] = min(s["n"], cfg["n"])
+    if budget_s is not None:
+        probe = dict(s, b=1, hq=1, hk=1)
+        ins = O.make_inputs(1, probe["n"], 1, 1, probe["d"], seed=1)
+        t0 = time.perf_counter()
+        O.two_simplicial_fwd_bwd(*ins, probe["w1"], probe["w2"], chunk=32)
+        per_pair = time.perf_counter() - t0
+        # the probe itself used every thread; more pairs parallelise better, credit at most 4x (1x on one core)
+        gain = float(min(4, torch.get_num_threads()))
+        pairs = int(budget_s / max(1, warmup + steps) / max(per_pair / gain, 1e-3))
+        pairs = max(1, min(16, pairs))
+        s["b"], s["hq"], s["hk"] = 1, pairs, pairs
     ins = O.make_inputs(s["b"], s["n"], s["hq"], s["hk"], s["d"], seed=1)
     times = []
     for it in range(warmup + steps):
@@ -206,14 +224,16 @@ def cpu_oracle_sample(cfg, steps=1, warmup=0):
 
 
 def run_reference(args, cfg, name):
+    """The reference arm: the CPU path of the operator (the oracle port of the reference's naive PyTorch
+    implementation) on this machine's host cores.  Rank 0 alone runs it; the other ranks exit at once."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = torch.get_num_threads()
-    tf, sec, desc, s = cpu_oracle_sample(cfg, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    threads = host_threads()
+    tf, sec, desc, s = cpu_oracle_sample(cfg, steps=max(1, args.steps), warmup=min(args.warmup, 1), budget_s=150.0)
     line = {
         "impl": "reference", "metric": "2-simplicial attn fwd+bwd TFLOP/s", "value": tf, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, **cfg, "sample": f"b{s['b']} h{s['hq']} n{s['n']}"},
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": desc,
@@ -296,6 +316,159 @@ def run_c4(args):
         torch.distributed.destroy_process_group()
 
 
+def load_traffic():
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the tensor-core kernels, taken
+    from the ncu captures summarised under profiles/ and scaled to a full launch where the capture was a
+    smaller case.  Keyed by "<workload>:<kernel>"."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return {}
+
+
+def timed_operator(sa, _lib, tensors, w1, w2, kernel, steps, flush):
+    """Per-step CUDA-event timing on the current stream, L2 flushed between steps: the forward and the
+    backward entry points as a user calls them."""
+    q, k1, k2, v1, v2, do = tensors
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    for s in range(steps):
+        flush.zero_()
+        ev[s][0].record()
+        out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=kernel)
+        ev[s][1].record()
+        sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=kernel)
+        ev[s][2].record()
+    torch.cuda.synchronize()
+    return [e[0].elapsed_time(e[1]) for e in ev], [e[1].elapsed_time(e[2]) for e in ev]
+
+
+def timed_kernels(sa, _lib, tensors, w1, w2, kernel, steps, flush):
+    """The backward's kernels timed apart, live, with CUDA events on the launching stream (the phases of
+    sa2_bwd are launched one by one; L2 flushed before each): milliseconds per launch of the row sums, the
+    dK1/dV1 kernel and the dQ/dK2/dV2 kernel (+ its reduction)."""
+    q, k1, k2, v1, v2, do = tensors
+    out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=kernel)
+    call = sa.BackwardCall(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=kernel)
+    call.launch(0)
+    res = {}
+    for name, phase in (("rowsum", _lib.BWD_ROWSUM), ("dk1_dv1", _lib.BWD_K1), ("dq_dk2_dv2", _lib.BWD_Q)):
+        ms = []
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            call.launch(phase)
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        res[name] = statistics.mean(ms)
+    return res
+
+
+def seq_record(sa, cfg, kernel, steps, world, rank, dev, flush):
+    """The same per-rank tensors as ONE sequence of length n * N split into consecutive blocks, one per
+    rank, with the key/value halo exchanged over NCCL (simplicial_attention_b200/shard.py)."""
+    from simplicial_attention_b200 import shard
+    import torch.distributed as dist
+    w1, w2 = cfg["w1"], cfg["w2"]
+    _, devt = make_inputs(cfg, seed=4321 + rank, dtype=torch.bfloat16, device=dev)
+    q, k1, k2, v1, v2, do = devt
+
+    def step():
+        leaves = [t.detach().requires_grad_() for t in (q, k1, k2, v1, v2)]
+        out = shard.sequence_parallel_attn(leaves[0], (leaves[1], leaves[2]), (leaves[3], leaves[4]), w1=w1, w2=w2, kernel=kernel)
+        out.backward(do)
+
+    for _ in range(3):
+        step()
+    barrier(world)
+    ms = []
+    for _ in range(steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    barrier(world)
+    step_ms = reduce_max(sum(ms), world) / steps
+    # the exchange alone (forward halos): events around the batched send/recv of the four tails
+    h1, h2, n = w1 - 1, w2 - 1, cfg["n"]
+    ex_ms = []
+    for _ in range(steps):
+        send = [k1[:, n - h1:].contiguous(), v1[:, n - h1:].contiguous(), k2[:, n - h2:].contiguous(), v2[:, n - h2:].contiguous()]
+        recv = [torch.empty_like(t) for t in send]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        e0.record()
+        ex = shard._Exchange(send if rank < world - 1 else None, rank + 1, recv if rank > 0 else None, rank - 1, None, "forward")
+        ex.wait(60.0)
+        e1.record()
+        torch.cuda.synchronize()
+        ex_ms.append(e0.elapsed_time(e1))
+    exchange_ms = reduce_max(statistics.median(ex_ms), world)
+    whole = dict(cfg, n=cfg["n"] * world)
+    fl = work_flops(whole)["fwd_bwd"]
+    halo_bytes = 2 * cfg["b"] * cfg["hk"] * cfg["d"] * 2 * (h1 + h2)
+    return {"sharding": "sequence blocks, one NCCL send/recv batch of the w1-1 / w2-1 row halo per direction, overlapped with the interior rows",
+            "sequence": cfg["n"] * world, "ms_per_step": step_ms, "value": fl / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "tokens_per_s": cfg["b"] * cfg["n"] * world / (step_ms * 1e-3),
+            "halo_bytes_per_boundary": halo_bytes, "exchange_ms": exchange_ms}
+
+
+def c5_record(sa, kernel, world, rank, dev, flush, steps=2):
+    """Strong scaling of the long-sequence configuration (b8 h16 n16384 d128, w 512/32): ONE problem split
+    over the N ranks by batch (no communication) and, for N > 1, by sequence blocks with the halo exchange."""
+    cfg = dict(WORKLOADS["C5"])
+    if cfg["b"] % world:
+        return {"skipped": f"batch {cfg['b']} does not divide over {world} ranks"}
+    fl = work_flops(cfg)["fwd_bwd"]
+    w1, w2 = cfg["w1"], cfg["w2"]
+    rec = {"config": dict(cfg), "scaling": "strong", "unit": "TFLOP/s"}
+
+    def run(local, fn):
+        _, devt = make_inputs(local, seed=555 + rank, dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            fn(devt)
+        barrier(world)
+        ms = []
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(devt)
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        barrier(world)
+        del devt
+        torch.cuda.empty_cache()
+        return reduce_max(sum(ms), world) / steps
+
+    def batch_step(t):
+        q, k1, k2, v1, v2, do = t
+        out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=kernel)
+        sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=kernel)
+
+    ms = run(dict(cfg, b=cfg["b"] // world), batch_step)
+    rec["batch_split"] = {"ms_per_step": ms, "value": fl / (ms * 1e-3) / 1e12, "tokens_per_s": cfg["b"] * cfg["n"] / (ms * 1e-3)}
+    if world > 1 and cfg["n"] % world == 0:
+        from simplicial_attention_b200 import shard
+
+        def seq_step(t):
+            leaves = [x.detach().requires_grad_() for x in t[:5]]
+            out = shard.sequence_parallel_attn(leaves[0], (leaves[1], leaves[2]), (leaves[3], leaves[4]), w1=w1, w2=w2, kernel=kernel)
+            out.backward(t[5])
+
+        ms = run(dict(cfg, n=cfg["n"] // world), seq_step)
+        rec["sequence_split"] = {"ms_per_step": ms, "value": fl / (ms * 1e-3) / 1e12, "tokens_per_s": cfg["b"] * cfg["n"] / (ms * 1e-3),
+                                 "halo_bytes_per_boundary": 2 * cfg["b"] * cfg["hk"] * cfg["d"] * 2 * (w1 - 1 + w2 - 1)}
+    return rec
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -304,11 +477,9 @@ def main():
     ap.add_argument("--workload", default="C3", choices=sorted(WORKLOADS) + ["C4"])
     ap.add_argument("--kernel", default="auto", choices=("auto", "simt", "tcgen05"))
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    ap.add_argument("--sharding", default="batch", choices=("batch", "seq"),
-                    help="batch: every rank runs its own batch (no collective); seq: the ranks hold consecutive blocks "
-                         "of one sequence of length n * N and exchange the key/value halo over NCCL")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the sequence-sharded and long-sequence records")
     args = ap.parse_args()
     if args.workload == "C4":
         if args.impl == "reference":
@@ -337,158 +508,139 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     dtype = torch.bfloat16
-    host, devt = make_inputs(cfg, seed=1234 + rank, dtype=dtype, device=dev, pin=True)
-    q, k1, k2, v1, v2, do = devt
+    big = args.workload == "C5"
+    host, devt = make_inputs(cfg, seed=1234 + rank, dtype=dtype, device=dev, pin=not (args.no_e2e or big))
     w1, w2 = cfg["w1"], cfg["w2"]
     fl = work_flops(cfg)
-    seq = args.sharding == "seq" and world > 1
-    if seq:
-        # one sequence of length n * world: per-rank share of its unmasked triples
-        whole = dict(cfg, n=cfg["n"] * world)
-        fl = {k: v / world for k, v in work_flops(whole).items()}
-        from simplicial_attention_b200 import shard
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
-
-    def seq_forward(leaves):
-        return shard.sequence_parallel_attn(leaves[0], (leaves[1], leaves[2]), (leaves[3], leaves[4]),
-                                            w1=w1, w2=w2, kernel=args.kernel)
-
-    def step_resident():
-        if seq:
-            leaves = [t.detach().requires_grad_() for t in (q, k1, k2, v1, v2)]
-            out = seq_forward(leaves)
-            out.backward(do)
-            return out, [t.grad for t in leaves]
-        out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=args.kernel)
-        return out, sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=args.kernel)
-
-    def timed_resident(steps):
-        """Per-step CUDA-event timing on the current stream, L2 flushed between steps."""
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
-        for s in range(steps):
-            flush.zero_()
-            ev[s][0].record()
-            if seq:
-                leaves = [t.detach().requires_grad_() for t in (q, k1, k2, v1, v2)]
-                out = seq_forward(leaves)          # includes the halo exchange
-                ev[s][1].record()
-                out.backward(do)                   # includes the exchange of the halo gradients
-            else:
-                out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=args.kernel)
-                ev[s][1].record()
-                sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=args.kernel)
-            ev[s][2].record()
-        torch.cuda.synchronize()
-        fwd = [e[0].elapsed_time(e[1]) for e in ev]
-        bwd = [e[1].elapsed_time(e[2]) for e in ev]
-        return fwd, bwd
-
-    dq_h = [torch.empty_like(t) for t in host[:5]]
-    out_h = torch.empty_like(host[0])
-    dq_h = [t.pin_memory() for t in dq_h]
-    out_h = out_h.pin_memory()
-
-    pipe = None
-    if not seq:
-        from simplicial_attention_b200.host import HostPipeline
-        pipe = HostPipeline(dev, w1=w1, w2=w2, chunk=max(1, cfg["b"] // 2), kernel=args.kernel)
-
-    def step_e2e():
-        if pipe is not None:
-            # batch chunks on three streams: copy-in, compute and copy-out overlap, also across steps
-            pipe.run(host, [out_h] + dq_h)
-            return
-        ins = [t.to(dev, non_blocking=True) for t in host]
-        leaves = [t.requires_grad_() for t in ins[:5]]
-        out = seq_forward(leaves) if seq else sa.sliding_two_simplicial_attn(
-            leaves[0], (leaves[1], leaves[2]), (leaves[3], leaves[4]), w1=w1, w2=w2, causal=True, kernel=args.kernel)
-        out.backward(ins[5])
-        out_h.copy_(out.detach(), non_blocking=True)
-        for h_, l_ in zip(dq_h, leaves):
-            h_.copy_(l_.grad, non_blocking=True)
-
-    h2d = sum(t.numel() * t.element_size() for t in host)
-    d2h = sum(t.numel() * t.element_size() for t in dq_h + [out_h])
+    steps = args.steps
+    warmup = max(3, args.warmup)
 
     # ---- warm-up
-    for _ in range(max(3, args.warmup)):
-        step_resident()
+    for _ in range(warmup):
+        out, lse = sa.sa2_forward(*devt[:5], w1, w2, kernel=args.kernel)
+        sa.sa2_backward(*devt[:5], out, lse, devt[5], w1, w2, kernel=args.kernel)
     torch.cuda.synchronize()
+    sa.check_device()
 
     # ---- timed, inputs resident in HBM
     sampler = ClockSampler(local)
     barrier(world)
     if rank == 0:
         sampler.start()
-    fwd_ms, bwd_ms = timed_resident(args.steps)
+    fwd_ms, bwd_ms = timed_operator(sa, _lib, devt, w1, w2, args.kernel, steps, flush)
     barrier(world)
     total_ms = reduce_max(sum(fwd_ms) + sum(bwd_ms), world)
     clocks = sampler.stop() if rank == 0 else None
+    kern_ms = timed_kernels(sa, _lib, devt, w1, w2, args.kernel, min(steps, 5), flush)
 
-    # ---- timed, end to end through the autograd API with host buffers
-    e2e_ms = float("nan")
-    if not args.no_e2e:
+    # ---- timed, end to end from pinned host buffers (copies inside the timed region)
+    e2e = None
+    if not (args.no_e2e or big):
+        from simplicial_attention_b200.host import HostPipeline
+        outs_h = [torch.empty_like(t).pin_memory() for t in [host[0]] + host[:5]]
+        pipe = HostPipeline(dev, w1=w1, w2=w2, chunk=max(1, cfg["b"] // 2), kernel=args.kernel)
         for _ in range(2):
-            step_e2e()
-        if pipe is not None:
-            pipe.synchronize()
+            pipe.run(host, outs_h)
+        pipe.synchronize()
+        pipe.record_copies()
         barrier(world)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps):
-            step_e2e()
-        if pipe is not None:
-            pipe.join()
+        for _ in range(steps):
+            pipe.run(host, outs_h)      # batch chunks on three streams: copy-in, compute and copy-out overlap, also across steps
+        pipe.join()
         e1.record()
         barrier(world)
-        e2e_ms = reduce_max(e0.elapsed_time(e1), world)
+        e2e_ms = reduce_max(e0.elapsed_time(e1), world) / steps
+        pipe.synchronize()
+        cs = pipe.copy_stats()
+        gbs = torch.tensor([cs["h2d_gbs"] or 0.0, cs["d2h_gbs"] or 0.0], dtype=torch.float64, device=dev)
+        if world > 1:
+            lo = gbs.clone()
+            torch.distributed.all_reduce(lo, op=torch.distributed.ReduceOp.MIN)
+            gbs = lo
+        e2e = {"value": fl["fwd_bwd"] * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host),
+               "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in outs_h),
+               "ms_per_step": e2e_ms, "h2d_gbs_min_rank": gbs[0].item(), "d2h_gbs_min_rank": gbs[1].item(),
+               "note": "throughput of back-to-back pipelined calls (copies of step s+1 overlap the kernels of step s), "
+                       "not the latency of one call; GB/s = bytes / time the copy stream was busy, slowest rank"}
+        del pipe, outs_h
+
+    # ---- extra records: the partitioned multi-GPU paths
+    seq = c5 = None
+    if not args.no_extra and not big:
+        del devt
+        torch.cuda.empty_cache()
+        if world > 1:
+            seq = seq_record(sa, cfg, args.kernel, min(steps, 5), world, rank, dev, flush)
+        c5 = c5_record(sa, args.kernel, world, rank, dev, flush)
+    status = sa.device_status()
 
     if rank != 0:
         if world > 1:
             torch.distributed.destroy_process_group()
         return
 
-    peaks = measured_peaks()
-    ms_per_step = total_ms / args.steps
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as f:
+            m = json.load(f)
+        burst, sustained, hbm, psrc = float(m["bf16_tflops"]), float(m.get("bf16_tflops_sustained") or m["bf16_tflops"]), float(m["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    else:
+        burst, sustained, hbm, psrc = 1590.0, 1400.0, 6650.0, "fallback (earlier measurement on this pool)"
+    ms_per_step = total_ms / steps
     value = fl["fwd_bwd"] * world / (ms_per_step * 1e-3) / 1e12
-    e2e_value = fl["fwd_bwd"] * world / (e2e_ms / args.steps * 1e-3) / 1e12
     shape = _lib.Shape(cfg["b"], cfg["n"], cfg["hq"], cfg["hk"], cfg["d"], w1, w2, 0, 0, _lib.SA2_BF16,
                        _lib.KERNELS[args.kernel], cfg["d"] ** -0.5)
     lib = _lib.lib()
     launches = lib.sa2_kernel_launches(ctypes.byref(shape), 0) + lib.sa2_kernel_launches(ctypes.byref(shape), 1)
     fwd_avg, bwd_avg = statistics.mean(fwd_ms), statistics.mean(bwd_ms)
-    fwd_tf = fl["fwd"] / (fwd_avg * 1e-3) / 1e12
-    bwd_tf = fl["bwd"] / (bwd_avg * 1e-3) / 1e12
+    # algorithmic work per kernel: forward 2 GEMM-equivalents (4 d per triple); of the backward's 5, the dK1/dV1
+    # kernel owns 2 (4 d) and the dQ/dK2/dV2 kernel 3 (6 d); recomputed products count zero
+    kernels = {
+        "fwd": {"ms": fwd_avg, "flops": fl["fwd"]},
+        "dk1_dv1": {"ms": kern_ms["dk1_dv1"], "flops": fl["bwd"] * 0.4},
+        "dq_dk2_dv2": {"ms": kern_ms["dq_dk2_dv2"], "flops": fl["bwd"] * 0.6},
+    }
+    for k in kernels.values():
+        k["tflops"] = k["flops"] / (k["ms"] * 1e-3) / 1e12
+        k["frac_of_burst"] = k["tflops"] / burst
+    top = max(kernels, key=lambda k: kernels[k]["ms"])
+    traffic = load_traffic()
     min_bytes = {"fwd": 6 * cfg["b"] * cfg["n"] * cfg["hq"] * cfg["d"] * 2, "bwd": 12 * cfg["b"] * cfg["n"] * cfg["hq"] * cfg["d"] * 2}
-
-    # DRAM bytes per launch from the ncu captures summarised under profiles/ (C3, tensor-core kernels):
-    # backward = dK1/dV1 kernel 115.6 MB + dQ/dK2/dV2 kernel 293.4 MB; forward 91.4 MB
-    traffic_bwd = 409.0e6 if (args.workload == "C3" and args.kernel == "auto" and not seq) else None
-    traffic_fwd = 91.4e6 if (args.workload == "C3" and args.kernel == "auto" and not seq) else None
     line = {
         "metric": "2-simplicial attn fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, **cfg, "global_batch": cfg["b"] * world, "kernel": args.kernel,
-                   "sharding": ("sequence blocks, NCCL send/recv of the w1-1 / w2-1 row halo" if seq
-                                else "batch x head per rank, no collective"),
+                   "sharding": "batch x head per rank, no collective",
                    "l2": "256 MB buffer written between timed steps"},
         "tokens_per_s": cfg["b"] * cfg["n"] * world / (ms_per_step * 1e-3),
-        "e2e": None if args.no_e2e else {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": launches * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "sa2_bwd", "achieved": bwd_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": bwd_tf / peaks["tflops"], "traffic": traffic_bwd, "peak_source": peaks["source"],
-                     "ms_per_launch": bwd_avg},
-        "roofline_fwd": {"bound": "tensor", "kernel": "sa2_fwd", "achieved": fwd_tf, "peak": peaks["tflops"],
-                         "unit": "TFLOP/s", "frac": fwd_tf / peaks["tflops"], "traffic": traffic_fwd, "ms_per_launch": fwd_avg},
+        "e2e": e2e,
+        "gpu_launches": launches * steps,
+        "roofline": {"bound": "tensor", "kernel": top, "achieved": kernels[top]["tflops"], "peak": burst, "unit": "TFLOP/s",
+                     "frac": kernels[top]["tflops"] / burst, "frac_of_sustained": kernels[top]["tflops"] / sustained,
+                     "peak_sustained": sustained, "traffic": traffic.get(f"{args.workload}:{top}"),
+                     "peak_source": psrc + ": cuBLAS bf16 burst; the sustained figure beside it",
+                     "ms_per_launch": kernels[top]["ms"]},
+        "kernels": {k: {"ms_per_launch": v["ms"], "tflops": v["tflops"], "frac_of_burst": v["frac_of_burst"],
+                        "traffic": traffic.get(f"{args.workload}:{k}")} for k, v in kernels.items()},
+        "step_frac_of_burst": value / world / burst,
+        "rowsum_ms": kern_ms["rowsum"],
         "hbm_min_gbs": {"fwd": min_bytes["fwd"] / (fwd_avg * 1e-3) / 1e9, "bwd": min_bytes["bwd"] / (bwd_avg * 1e-3) / 1e9,
-                        "peak": peaks["hbm_gbs"]},
-        "clocks": clocks,
+                        "peak": hbm},
+        "clocks": clocks, "device_status": status,
     }
+    if seq is not None:
+        line["seq"] = seq
+    if c5 is not None:
+        line["c5"] = c5
     if world == 1 and not args.no_cpu_baseline:
-        tf, sec, desc, _ = cpu_oracle_sample(cfg)
-        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+        threads = host_threads()
+        tf, sec, desc, _ = cpu_oracle_sample(cfg, budget_s=25.0)
+        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                 "sample": desc, "host_cpus": os.cpu_count()}
     print(json.dumps(line), flush=True)
     if world > 1:

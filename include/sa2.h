@@ -70,6 +70,14 @@ typedef struct sa2_shape {
     float   scale;    /* logit scale; the reference uses d^-0.5 */
 } sa2_shape;
 
+/*
+ * Parts of the backward that sa2_bwd_args.phases can select (0 runs all of them).  ROWSUM writes
+ * D_i = sum_c O_ic dO_ic into the workspace; K1 (dK1, dV1) and Q (dQ, dK2, dV2) read it and are
+ * independent of each other, so a caller may time them apart or run them on different streams
+ * after ROWSUM has been ordered before both.
+ */
+typedef enum sa2_bwd_phase { SA2_BWD_ROWSUM = 1, SA2_BWD_K1 = 2, SA2_BWD_Q = 4 } sa2_bwd_phase;
+
 typedef struct sa2_fwd_args {
     sa2_shape shape;
     const void *q, *k1, *k2, *v1, *v2;
@@ -89,7 +97,7 @@ typedef struct sa2_bwd_args {
     void *dk2, *dv2;          /* [b][n+off2][hk][d] */
     sa2_strides sq, sk1, sk2, sv1, sv2, sout, sdout, sdq, sdk1, sdk2, sdv1, sdv2;
     int32_t grad_dtype;       /* sa2_dtype of dq, dk1, dk2, dv1, dv2 */
-    int32_t reserved;
+    int32_t phases;           /* 0: the whole backward; otherwise an OR of sa2_bwd_phase */
     void  *workspace;         /* >= sa2_bwd_workspace_bytes(&shape) bytes, 256-byte aligned */
     size_t workspace_bytes;
     void *stream;
@@ -160,12 +168,20 @@ int sa2_kernel_launches(const sa2_shape *shape, int backward);
 /*
  * Device status word of the current device: 0 when every kernel ran to
  * completion, otherwise the OR of the error bits of kernels that gave up on a
- * bounded wait (their outputs are then undefined).  Synchronises the device;
+ * bounded wait (the rows they owned are then written as NaN).  Synchronises the device;
  * meant for tests and diagnostics, not for the hot path.  `reset` != 0 clears
  * the word.  Returns -1 if the word cannot be read.  No counterpart in the
  * reference, whose Triton kernels contain no waits.
  */
 int sa2_device_status(int reset);
+
+/*
+ * The same check as a status: SA2_OK when the status word is 0, SA2_ERR_DEVICE
+ * when a kernel gave up on a bounded wait since the last reset (the rows that
+ * kernel owned were written as NaN), SA2_ERR_CUDA if the word cannot be read.
+ * Synchronises the device.  No counterpart in the reference.
+ */
+int sa2_check_device(int reset);
 
 /* Static, human-readable text for a status code. */
 const char *sa2_strerror(int status);

@@ -6,7 +6,9 @@ Drop-in for the sliding path of lucidrains/simplicial-attention:
 hand-written sm_100a CUDA kernels behind the C ABI of ``include/sa2.h``.
 """
 from .attention import (
+    BackwardCall,
     SlidingTwoSimplicialAttention,
+    check_device,
     device_status,
     sa2_backward,
     sa2_forward,
@@ -23,6 +25,8 @@ __all__ = [
     "sa2_forward",
     "sa2_backward",
     "device_status",
+    "check_device",
+    "BackwardCall",
     "HostPipeline",
     "HigherOrderAttention",
     "SlidingWindowTwoSimplicialMHA",

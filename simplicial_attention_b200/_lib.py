@@ -14,10 +14,11 @@ SA2_OK = 0
 SA2_F32, SA2_BF16 = 0, 1
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
 KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "tcgen05": KERNEL_TCGEN05}
+BWD_ROWSUM, BWD_K1, BWD_Q = 1, 2, 4     # sa2_bwd_phase
 
 # symbols declared in include/sa2.h
 EXPORTS = ("sa2_fwd", "sa2_bwd", "sa2_bwd_workspace_bytes", "sa2_strerror", "sa2_version",
-           "sa2_kernel_launches", "sa2_device_status", "sa2_bwd_static_scratch",
+           "sa2_kernel_launches", "sa2_device_status", "sa2_check_device", "sa2_bwd_static_scratch",
            "sa2_headnorm_fwd", "sa2_headnorm_bwd", "sa2_headnorm_partial_bytes")
 STATIC_SCRATCH_ROWS = 262144   # SA2_STATIC_SCRATCH_ROWS in include/sa2.h
 
@@ -53,7 +54,7 @@ class BwdArgs(C.Structure):
         ("sq", Strides), ("sk1", Strides), ("sk2", Strides), ("sv1", Strides), ("sv2", Strides),
         ("sout", Strides), ("sdout", Strides), ("sdq", Strides),
         ("sdk1", Strides), ("sdk2", Strides), ("sdv1", Strides), ("sdv2", Strides),
-        ("grad_dtype", C.c_int32), ("reserved", C.c_int32),
+        ("grad_dtype", C.c_int32), ("phases", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("stream", C.c_void_p),
     ]
@@ -86,8 +87,8 @@ def lib() -> C.CDLL:
         if _lib is not None:
             return _lib
         path = lib_path()
-        if not os.path.exists(path) or os.environ.get("SA2_REBUILD"):
-            from . import build
+        from . import build
+        if os.environ.get("SA2_REBUILD") or build.is_stale():
             build.build(force=bool(os.environ.get("SA2_REBUILD")))
         handle = C.CDLL(path)
         handle.sa2_fwd.argtypes = [C.POINTER(FwdArgs)]
@@ -102,6 +103,8 @@ def lib() -> C.CDLL:
         handle.sa2_kernel_launches.restype = C.c_int
         handle.sa2_device_status.argtypes = [C.c_int]
         handle.sa2_device_status.restype = C.c_int
+        handle.sa2_check_device.argtypes = [C.c_int]
+        handle.sa2_check_device.restype = C.c_int
         handle.sa2_strerror.argtypes = [C.c_int]
         handle.sa2_strerror.restype = C.c_char_p
         handle.sa2_headnorm_fwd.argtypes = [C.POINTER(HeadnormArgs)]

@@ -57,11 +57,14 @@ int simt_fwd(const KernelParams &p, cudaStream_t st) {
 }
 
 template <int D>
-int simt_bwd(const KernelParams &p, cudaStream_t st) {
+int simt_bwd(const KernelParams &p, cudaStream_t st, int phases = 0) {
     using namespace sa2::simt;
-    const int64_t rows = (int64_t)p.b * p.n * p.hq;
-    delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(p, D);
-    if (int e = launch_status()) return e;
+    if (phases == 0) phases = SA2_BWD_ROWSUM | SA2_BWD_K1 | SA2_BWD_Q;
+    if (phases & SA2_BWD_ROWSUM) {
+        const int64_t rows = (int64_t)p.b * p.n * p.hq;
+        delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(p, D);
+        if (int e = launch_status()) return e;
+    }
 
     auto kq = row_kernel<D, MODE_BWD_Q>;
     auto kk2 = row_kernel<D, MODE_BWD_K2>;
@@ -70,12 +73,17 @@ int simt_bwd(const KernelParams &p, cudaStream_t st) {
     if (int e = set_smem(kk2, Cfg<D>::smem_bwd)) return e;
     if (int e = set_smem(kk1, Cfg<D>::smem_bwd)) return e;
 
-    kq<<<dim3((p.n + TILE - 1) / TILE, p.hq, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
-    if (int e = launch_status()) return e;
-    kk2<<<dim3((p.nk2 + TILE - 1) / TILE, p.hk, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
-    if (int e = launch_status()) return e;
-    kk1<<<dim3((p.nk1 + TILE - 1) / TILE, p.hk, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
-    return launch_status();
+    if (phases & SA2_BWD_Q) {
+        kq<<<dim3((p.n + TILE - 1) / TILE, p.hq, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
+        if (int e = launch_status()) return e;
+        kk2<<<dim3((p.nk2 + TILE - 1) / TILE, p.hk, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
+        if (int e = launch_status()) return e;
+    }
+    if (phases & SA2_BWD_K1) {
+        kk1<<<dim3((p.nk1 + TILE - 1) / TILE, p.hk, p.b), NTHREADS, Cfg<D>::smem_bwd, st>>>(p);
+        return launch_status();
+    }
+    return SA2_OK;
 }
 
 }  // namespace
@@ -83,13 +91,6 @@ int simt_bwd(const KernelParams &p, cudaStream_t st) {
 extern "C" {
 
 int sa2_version(void) { return 100; }
-
-#ifdef SA2_TRACE
-// diagnostic builds only: copy the timeline stamps of the traced forward CTA to the host
-int sa2_trace_read(unsigned long long *host, int n) {
-    return cudaMemcpyFromSymbol(host, sa2::tc::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int sa2_device_status(int reset) {
     int *word = sa2::tc::status_word();
@@ -103,6 +104,12 @@ int sa2_device_status(int reset) {
     return v;
 }
 
+int sa2_check_device(int reset) {
+    const int v = sa2_device_status(reset);
+    if (v < 0) return SA2_ERR_CUDA;
+    return v == 0 ? SA2_OK : SA2_ERR_DEVICE;
+}
+
 const char *sa2_strerror(int status) {
     switch (status) {
         case SA2_OK: return "ok";
@@ -111,7 +118,7 @@ const char *sa2_strerror(int status) {
                                          "the tcgen05 kernels need bf16)";
         case SA2_ERR_WORKSPACE: return "workspace missing, misaligned or smaller than sa2_bwd_workspace_bytes()";
         case SA2_ERR_CUDA: return "a CUDA call failed";
-        case SA2_ERR_DEVICE: return "a kernel gave up on a bounded wait";
+        case SA2_ERR_DEVICE: return "a kernel gave up on a bounded wait; the rows it owned hold NaN";
         case SA2_ERR_TOO_LARGE: return "problem too large for the library's built-in scratch: b * hq * n exceeds "
                                        "SA2_STATIC_SCRATCH_ROWS (use sa2_bwd with a caller-provided workspace)";
         default: return "unknown status";
@@ -166,6 +173,7 @@ int sa2_bwd(const sa2_bwd_args *a) {
     if (!a->q || !a->k1 || !a->k2 || !a->v1 || !a->v2 || !a->out || !a->dout || !a->lse) return SA2_ERR_INVALID;
     if (!a->dq || !a->dk1 || !a->dk2 || !a->dv1 || !a->dv2) return SA2_ERR_INVALID;
     if (a->grad_dtype != SA2_F32 && a->grad_dtype != SA2_BF16) return SA2_ERR_UNSUPPORTED;
+    if (a->phases < 0 || a->phases > (SA2_BWD_ROWSUM | SA2_BWD_K1 | SA2_BWD_Q)) return SA2_ERR_INVALID;
     const void *ptrs[] = {a->q, a->k1, a->k2, a->v1, a->v2, a->out, a->dout, a->dq, a->dk1, a->dk2, a->dv1, a->dv2};
     for (const void *p : ptrs) if (!aligned16(p)) return SA2_ERR_INVALID;
     const sa2_strides *ss[] = {&a->sq, &a->sk1, &a->sk2, &a->sv1, &a->sv2, &a->sout, &a->sdout,
@@ -192,13 +200,13 @@ int sa2_bwd(const sa2_bwd_args *a) {
     if (tc_ok && a->shape.kernel != SA2_KERNEL_SIMT) {
         size_t delta = (size_t)a->shape.b * a->shape.hq * a->shape.n * sizeof(float);
         delta = (delta + 255) & ~(size_t)255;
-        return sa2::tc::bwd(p, a->shape, reinterpret_cast<char *>(a->workspace) + delta, st);
+        return sa2::tc::bwd(p, a->shape, reinterpret_cast<char *>(a->workspace) + delta, st, a->phases);
     }
 
     switch (a->shape.d) {
-        case 32: return simt_bwd<32>(p, st);
-        case 64: return simt_bwd<64>(p, st);
-        default: return simt_bwd<128>(p, st);
+        case 32: return simt_bwd<32>(p, st, a->phases);
+        case 64: return simt_bwd<64>(p, st, a->phases);
+        default: return simt_bwd<128>(p, st, a->phases);
     }
 }
 
@@ -331,7 +339,8 @@ int headnorm_launch(const sa2_headnorm_args *a, const sa2::headnorm::Params &P, 
 int headnorm_dispatch(const sa2_headnorm_args *a, bool backward) {
     const int rc = headnorm_check(a, backward);
     if (rc != SA2_OK) return rc;
-    if ((size_t)sa2::headnorm::WARPS * a->channels * sizeof(float) > 200 * 1024) return SA2_ERR_UNSUPPORTED;
+    // only the backward keeps per-warp partial rows of the gain gradient in shared memory
+    if (backward && (size_t)sa2::headnorm::WARPS * a->channels * sizeof(float) > 200 * 1024) return SA2_ERR_UNSUPPORTED;
     sa2::headnorm::Params P;
     P.x = a->x; P.dy = a->dy; P.weight = a->weight; P.y = a->y; P.rstd = a->rstd;
     P.partial = reinterpret_cast<float *>(a->partial);

@@ -502,13 +502,13 @@ __global__ void __launch_bounds__(NTHREADS) k1_kernel(const KernelParams p) {
 
 // D_i = sum_c O_ic dO_ic, one warp per (b, i, h) row.
 __global__ void delta_kernel(const KernelParams p, int d) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int64_t rows = (int64_t)p.b * p.n * p.hq;
     if (warp >= rows) return;
-    const int h = warp % p.hq;
-    const int i = (warp / p.hq) % p.n;
-    const int b = warp / (p.hq * p.n);
+    const int h = (int)(warp % p.hq);
+    const int i = (int)((warp / p.hq) % p.n);
+    const int b = (int)(warp / ((int64_t)p.hq * p.n));
     const bool bf16 = p.in_bf16 != 0;
     float s = 0.f;
     for (int c = lane * 2; c < d; c += 64) {

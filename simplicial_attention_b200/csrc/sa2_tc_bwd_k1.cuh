@@ -163,9 +163,7 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
             }
             for (int e = 0; e < ne; ++e, ++s) {
                 const int stage = s % BK1_STAGES;
-                SA2_TRACE_MARK(r == 0 && s < 200, s * 4);
                 if (s >= BK1_STAGES && !warp_wait(&bars[BK1_AB_EMPTY + stage], (s / BK1_STAGES - 1) & 1, abort_flag)) return ERR_BK1_BUILDER;
-                SA2_TRACE_MARK(r == 0 && s < 200, s * 4 + 1);
                 if (e == 0) {
                     // Statistics of this query tile: two K = 16 slabs (-lse2/c, -D) of a four-slab tile; two
                     // such tiles hold the last four query tiles.  Step s - 3 has completed, and every tile has
@@ -203,7 +201,6 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&bars[BK1_AB_FULL + stage]);
-                SA2_TRACE_MARK(r == 0 && s < 200, s * 4 + 2);
             }
         }
     }
@@ -261,9 +258,7 @@ __device__ __forceinline__ int bk1_mma_second(const Bk1Geom &g, uint32_t tmem, u
         const int stage = s % BK1_STAGES;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            SA2_TRACE_MARK(s < 200, 3000 + (s * 2 + half) * 4);
             if (!mbar_wait(&bars[BK1_P_FULL + half], s & 1, abort_flag)) return ERR_BK1_MMA;
-            SA2_TRACE_MARK(s < 200, 3000 + (s * 2 + half) * 4 + 1);
             tc_fence_after();
             const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4), bq = a + (TILE_BYTES >> 4);
             const uint32_t t = tmem + 256 + half * 64;
@@ -277,7 +272,6 @@ __device__ __forceinline__ int bk1_mma_second(const Bk1Geom &g, uint32_t tmem, u
             mma_ts(tmem + 384, t + 48, a + 256, IDESC_G, 1u);
             mma_ts(tmem + 384, t + 56, a + 384, IDESC_G, 1u);
             tc_commit(&bars[BK1_G_DONE + half]);
-            SA2_TRACE_MARK(s < 200, 3000 + (s * 2 + half) * 4 + 2);
         }
         tc_commit(&bars[BK1_AB_EMPTY + stage]);
     }
@@ -298,65 +292,68 @@ __device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g,
     const bool jv = j < kp.nk1;
     const float c = P.c;
 
-    int s = 0, tile_counter = 0;
-    for (int hh = 0; hh < kp.g; ++hh) {
-        for (int t = 0; t < g.n_it; ++t, ++tile_counter) {
-            const int it0 = g.i_lo + TQ * t;
-            const int ne = bk1_sweeps(kp, g, t);
-            const int base = j - kp.off1 - it0;                       // column of the diagonal i + off1 == j
-            const int hi = (jv ? min(min(TQ - 1, base + kp.w1 - 1), g.i_hi - it0) : -1) - half * 64;
-            for (int e = 0; e < ne; ++e, ++s) {
-                const int lo = max(max(0, base), e - kp.off2 - it0) - half * 64;     // valid columns: lo <= col <= hi
-                SA2_TRACE_MARK(r == 0 && s < 200, 5000 + (s * 2 + half) * 4);
-                if (!warp_wait(&bars[BK1_S_FULL + half], s & 1, abort_flag)) return ERR_BK1_COMPUTE;
-                SA2_TRACE_MARK(r == 0 && s < 200, 5000 + (s * 2 + half) * 4 + 1);
-                tc_fence_after();
-                const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
-                // P^T / G^T of the previous step must have been consumed before they are overwritten
-                if (s >= 1 && !warp_wait(&bars[BK1_G_DONE + half], (s - 1) & 1, abort_flag)) return ERR_BK1_COMPUTE;
+    // the walk over the steps; a wait that runs out ends it early, the rows are then reported as NaN below
+    auto walk = [&]() -> int {
+        int s = 0, tile_counter = 0;
+        for (int hh = 0; hh < kp.g; ++hh) {
+            for (int t = 0; t < g.n_it; ++t, ++tile_counter) {
+                const int it0 = g.i_lo + TQ * t;
+                const int ne = bk1_sweeps(kp, g, t);
+                const int base = j - kp.off1 - it0;                       // column of the diagonal i + off1 == j
+                const int hi = (jv ? min(min(TQ - 1, base + kp.w1 - 1), g.i_hi - it0) : -1) - half * 64;
+                for (int e = 0; e < ne; ++e, ++s) {
+                    const int lo = max(max(0, base), e - kp.off2 - it0) - half * 64;     // valid columns: lo <= col <= hi
+                    if (!warp_wait(&bars[BK1_S_FULL + half], s & 1, abort_flag)) return ERR_BK1_COMPUTE;
+                    tc_fence_after();
+                    const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
+                    // P^T / G^T of the previous step must have been consumed before they are overwritten
+                    if (s >= 1 && !warp_wait(&bars[BK1_G_DONE + half], (s - 1) & 1, abort_flag)) return ERR_BK1_COMPUTE;
 #pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t sv[32], dv[32], pk[16], gk[16];
-                    tmem_ld32(buf + ch * 32, sv);
-                    tmem_ld32(buf + 64 + ch * 32, dv);
-                    tmem_wait_ld();
-                    // the accumulators already hold S^T - lse2 / c and dP^T - D
-                    if (full) {
+                    for (int ch = 0; ch < 2; ++ch) {
+                        uint32_t sv[32], dv[32], pk[16], gk[16];
+                        tmem_ld32(buf + ch * 32, sv);
+                        tmem_ld32(buf + 64 + ch * 32, dv);
+                        tmem_wait_ld();
+                        // the accumulators already hold S^T - lse2 / c and dP^T - D
+                        if (full) {
 #pragma unroll
-                        for (int x = 0; x < 32; x += 2) {
-                            const float p0 = ex2(__uint_as_float(sv[x]) * c);
-                            const float p1 = ex2(__uint_as_float(sv[x + 1]) * c);
-                            pk[x >> 1] = pack_bf16(p0, p1);
-                            gk[x >> 1] = pack_bf16(p0 * __uint_as_float(dv[x]), p1 * __uint_as_float(dv[x + 1]));
+                            for (int x = 0; x < 32; x += 2) {
+                                const float p0 = ex2(__uint_as_float(sv[x]) * c);
+                                const float p1 = ex2(__uint_as_float(sv[x + 1]) * c);
+                                pk[x >> 1] = pack_bf16(p0, p1);
+                                gk[x >> 1] = pack_bf16(p0 * __uint_as_float(dv[x]), p1 * __uint_as_float(dv[x + 1]));
+                            }
+                        } else {
+                            // valid columns are the integers in [lo, hi]: saturate(half + 1 - |col - mid|) is
+                            // exactly 1 inside and 0 outside (FMA pipe instead of compares and selects on the
+                            // ALU pipe); the exponent is clamped so that a masked-out cell cannot give inf * 0
+                            const float mid = 0.5f * (float)(lo + hi), hwp = 0.5f * (float)(hi - lo) + 1.f;
+#pragma unroll
+                            for (int x = 0; x < 32; x += 2) {
+                                const int col = ch * 32 + x;
+                                const float v0 = __saturatef(hwp - fabsf((float)col - mid));
+                                const float v1 = __saturatef(hwp - fabsf((float)(col + 1) - mid));
+                                const float p0 = ex2(fminf(__uint_as_float(sv[x]) * c, 100.f)) * v0;
+                                const float p1 = ex2(fminf(__uint_as_float(sv[x + 1]) * c, 100.f)) * v1;
+                                pk[x >> 1] = pack_bf16(p0, p1);
+                                gk[x >> 1] = pack_bf16(p0 * __uint_as_float(dv[x]), p1 * __uint_as_float(dv[x + 1]));
+                            }
                         }
-                    } else {
-                        // valid columns are the integers in [lo, hi]: saturate(half + 1 - |col - mid|) is
-                        // exactly 1 inside and 0 outside (FMA pipe instead of compares and selects on the
-                        // ALU pipe); the exponent is clamped so that a masked-out cell cannot give inf * 0
-                        const float mid = 0.5f * (float)(lo + hi), hwp = 0.5f * (float)(hi - lo) + 1.f;
-#pragma unroll
-                        for (int x = 0; x < 32; x += 2) {
-                            const int col = ch * 32 + x;
-                            const float v0 = __saturatef(hwp - fabsf((float)col - mid));
-                            const float v1 = __saturatef(hwp - fabsf((float)(col + 1) - mid));
-                            const float p0 = ex2(fminf(__uint_as_float(sv[x]) * c, 100.f)) * v0;
-                            const float p1 = ex2(fminf(__uint_as_float(sv[x + 1]) * c, 100.f)) * v1;
-                            pk[x >> 1] = pack_bf16(p0, p1);
-                            gk[x >> 1] = pack_bf16(p0 * __uint_as_float(dv[x]), p1 * __uint_as_float(dv[x + 1]));
-                        }
+                        tmem_st16(pg + ch * 16, pk);
+                        tmem_st16(pg + 32 + ch * 16, gk);
                     }
-                    tmem_st16(pg + ch * 16, pk);
-                    tmem_st16(pg + 32 + ch * 16, gk);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&bars[BK1_P_FULL + half]);
                 }
-                tmem_wait_st();
-                SA2_TRACE_MARK(r == 0 && s < 200, 5000 + (s * 2 + half) * 4 + 2);
-                tc_fence_before();
-                mbar_arrive(&bars[BK1_P_FULL + half]);
             }
         }
-    }
+        return 0;
+    };
+    int err = walk();
     // drain: group 0 writes dK1, group 1 writes dV1
-    if (!warp_wait(&bars[BK1_DONE], 0, abort_flag)) return ERR_BK1_COMPUTE;
+    if (err == 0 && !warp_wait(&bars[BK1_DONE], 0, abort_flag)) err = ERR_BK1_COMPUTE;
+    const bool bad = __any_sync(0xffffffffu, err != 0) || *abort_flag != 0;
     tc_fence_after();
     const bool gbf16 = kp.grad_bf16 != 0;
     const TensorRef &dst = half == 0 ? kp.dk1 : kp.dv1;
@@ -372,12 +369,12 @@ __device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g,
             for (int u = 0; u < 8; ++u) {
                 float x[4];
 #pragma unroll
-                for (int z = 0; z < 4; ++z) x[z] = (g.total > 0 ? __uint_as_float(w[u * 4 + z]) : 0.f) * mul;
+                for (int z = 0; z < 4; ++z) x[z] = bad ? CUDART_NAN_F : (g.total > 0 ? __uint_as_float(w[u * 4 + z]) : 0.f) * mul;
                 store_vec<4>(dst.p, off + u * 4, gbf16, x);
             }
         }
     }
-    return 0;
+    return err;
 }
 
 __global__ void __launch_bounds__(BK1_THREADS, 1)

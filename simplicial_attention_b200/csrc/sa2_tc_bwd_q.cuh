@@ -1,12 +1,21 @@
 // Backward kernel for dQ, dK2, dV2 on tcgen05 tensor cores (bf16 operands,
-// fp32 accumulation in TMEM, head dim 64), plus the reduction of its partials.
+// fp32 accumulation in TMEM, head dim 64 or 128), plus the reduction of its
+// partials.
 //
 // A CTA owns 128 query rows i of one (batch, query head) and a subset ("split")
-// of at most three 128-row K1/V1 tiles of their window, resident in shared
-// memory.  Because the backward recomputes probabilities from the saved
-// logsumexp, the splits of one query tile are independent; each writes fp32
-// partials to scratch and a small second kernel adds them in a fixed order
-// (splits, then the query heads of a kv group), so results are reproducible.
+// of the 128-row K1/V1 tiles of their window.  Because the backward recomputes
+// probabilities from the saved logsumexp, the splits of one query tile are
+// independent; each writes fp32 partials to scratch and a small second kernel
+// adds them in a fixed order (splits, then the query heads of a kv group), so
+// results are reproducible.
+// Head dim 64: a split keeps its (at most three) tiles resident in shared memory; a 5-tile window is
+// two splits.
+// Head dim 128: a CTA produces 64 of the 128 output channels (blockIdx.x also carries the channel
+// half): S and dP contract over all 128 channels, U and W use the 64-channel block of K1 / V1 as their
+// B operand, so the fold, its registers and the shared accumulators are those of head dim 64.  The
+// accumulators and the two 32 KB operand tiles leave room for 64 KB of K1 / V1 only, so one CTA walks
+// the whole window (one split) and its 64-row units stream through a two-slot TMA ring, once per
+// sweep, from L2: slot h serves TMEM half h and is refilled when the U / W products of its unit are done.
 //
 // Per offset e ("sweep") the builder warps form A_e = q_i * k2_{i-e} and
 // B_e = dO_i * v2_{i-e}; per 64-key half-tile the tensor cores compute
@@ -38,7 +47,17 @@ constexpr int BQ_THREADS = 512;
 // four budgets must add up to 4 * 128.
 constexpr int BQ_REGS_LAUNCH = 128, BQ_REGS_ISSUE = 40, BQ_REGS_COMPUTE = 120, BQ_REGS_FOLD = 192, BQ_REGS_BUILD = 160;
 static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BQ_REGS_FOLD + BQ_REGS_BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
-constexpr int BQ_MAX_TILES = 3;          // K1/V1 tiles resident per CTA
+template <int D> struct BqCfg {
+    static constexpr int CH = D / 64;                            // channel halves = CTAs per (query tile, split)
+    static constexpr int KSTEPS = D / 16;                        // K = 16 steps of S and dP
+    static constexpr uint32_t BLK = TJ * 128;                    // A_e / B_e: one [128 rows][64 channels] swizzled block
+    static constexpr uint32_t TILE = (D / 64) * BLK;             // A_e or B_e
+    // K1 / V1 in shared memory: head dim 64 keeps three 128-row tiles of 16 KB resident; head dim 128 has a
+    // ring of two 64-row units, each two [64 rows][64 channels] blocks of 8 KB
+    static constexpr uint32_t KV_BYTES = D == 64 ? 3 * BLK : 2 * 16384;
+    static constexpr uint32_t UBLK = 8192;                       // one channel block of a 64-row unit (head dim 128)
+};
+constexpr int BQ_MAX_TILES = 3;          // K1/V1 tiles of one split (head dim 64)
 constexpr int BQ_ACC_STRIDE = 68;        // floats per accumulator row (64 + 4: conflict-free row-per-thread access)
 constexpr int BQ_MAX_W2 = 56;            // the shared accumulators hold 127 + w2 rows; beyond this they do not fit
 
@@ -51,7 +70,8 @@ enum BqBar {
     BQ_W_FULL = 7,       // [2]
     BQ_W_EMPTY = 9,      // [2]
     BQ_G_DONE = 11,      // [2] per half: the U / W products of the unit have completed
-    BQ_BAR_COUNT = 13
+    BQ_KV_SLOT = 13,     // [2] head dim 128: the K1/V1 unit of the slot has landed
+    BQ_BAR_COUNT = 15
 };
 
 enum { ERR_BQ_PRODUCER = 256, ERR_BQ_MMA = 512, ERR_BQ_COMPUTE = 1024, ERR_BQ_BUILDER = 2048 };
@@ -63,44 +83,64 @@ struct BqParams {
     int nsplit;         // CTAs sharing one query tile
     int tiles_per_split;
     int nqt;            // query tiles
-    float *part_dq;     // [nsplit][b][n][hq][64]
-    float *part_k2;     // [b][hq][nqt][nsplit][2][acc_rows][64]   (dK2 slab, then dV2 slab)
+    float *part_dq;     // [nsplit][b][n][hq][d]
+    float *part_k2;     // [b][hq][nqt][nsplit][2][acc_rows][d]   (dK2 slab, then dV2 slab)
     int *status;
 };
 
 inline int bq_acc_rows(int w2) { return 127 + w2; }
-inline size_t bq_smem_bytes(int w2) {
-    return 1024 + (size_t)2 * BQ_MAX_TILES * TILE_BYTES + 2 * TILE_BYTES +
+template <int D> inline size_t bq_smem_bytes(int w2) {
+    return 1024 + (size_t)2 * BqCfg<D>::KV_BYTES + 2 * BqCfg<D>::TILE +
            (size_t)2 * bq_acc_rows(w2) * BQ_ACC_STRIDE * sizeof(float) + 256;
 }
-inline size_t bq_part_dq_bytes(const sa2_shape &s, int nsplit) { return (size_t)nsplit * s.b * s.n * s.hq * 64 * sizeof(float); }
+inline size_t bq_part_dq_bytes(const sa2_shape &s, int nsplit) { return (size_t)nsplit * s.b * s.n * s.hq * s.d * sizeof(float); }
 inline size_t bq_part_k2_bytes(const sa2_shape &s, int nsplit) {
     const size_t nqt = (s.n + TQ - 1) / TQ;
-    return (size_t)s.b * s.hq * nqt * nsplit * 2 * bq_acc_rows(s.w2) * 64 * sizeof(float);
+    return (size_t)s.b * s.hq * nqt * nsplit * 2 * bq_acc_rows(s.w2) * s.d * sizeof(float);
 }
 
 struct BqGeom {
-    int i0, i_last, jbase, t_begin, ntl, nsweeps, upe, total;
+    int qt, split, chh;          // query tile, split, channel half of this CTA
+    int i0, i_last, nsweeps;
+    int ubase;                   // first-key row of the CTA's unit 0; unit x covers rows ubase + 64 x ... + 63
+    int nunits;                  // 64-key units the CTA visits in every sweep
+    int total;                   // nunits * nsweeps
 };
 
+template <int D>
 __device__ __forceinline__ BqGeom bq_geom(const BqParams &P) {
     BqGeom g;
     const KernelParams &kp = P.kp;
-    const int qt = blockIdx.x / P.nsplit, split = blockIdx.x % P.nsplit;
-    g.i0 = qt * TQ;
+    g.chh = blockIdx.x % BqCfg<D>::CH;
+    const int qs = blockIdx.x / BqCfg<D>::CH;
+    g.qt = qs / P.nsplit;
+    g.split = qs % P.nsplit;
+    g.i0 = g.qt * TQ;
     g.i_last = min(g.i0 + TQ - 1, kp.n - 1);
-    g.jbase = g.i0 + kp.off1 + TJ - TJ * P.nt;
-    const int t_first = g.jbase >= 0 ? 0 : min(P.nt - 1, (-g.jbase) / TJ);
-    g.t_begin = max(t_first, split * P.tiles_per_split);
-    const int t_end = min(P.nt, (split + 1) * P.tiles_per_split);
-    g.ntl = max(0, t_end - g.t_begin);
     g.nsweeps = min(kp.w2, g.i_last + kp.off2 + 1);
-    g.upe = g.ntl * 2;
-    g.total = g.upe * g.nsweeps;
+    if constexpr (D == 64) {
+        const int jbase = g.i0 + kp.off1 + TJ - TJ * P.nt;        // tile t covers rows jbase + 128 t ...
+        const int t_first = jbase >= 0 ? 0 : min(P.nt - 1, (-jbase) / TJ);
+        const int t_begin = max(t_first, g.split * P.tiles_per_split);
+        const int t_end = min(P.nt, (g.split + 1) * P.tiles_per_split);
+        g.ubase = jbase + TJ * t_begin;
+        g.nunits = 2 * max(0, t_end - t_begin);
+    } else {
+        const int nh = (kp.w1 + TQ - 1 + 63) / 64;                // 64-row units of the window: ceil((w1 + 127) / 64)
+        const int hbase = g.i0 + kp.off1 + TQ - 64 * nh;
+        const int h_first = hbase >= 0 ? 0 : min(nh - 1, (-hbase) / 64);
+        g.ubase = hbase + 64 * h_first;
+        g.nunits = nh - h_first;
+    }
+    g.total = g.nunits * g.nsweeps;
     return g;
 }
 
 // ---------------------------------------------------------------- builders (warps 12-15)
+// One thread per query row forms row r of A_e and B_e for every sweep.  Head dim 64 keeps the
+// q / dO rows in registers; head dim 128 reads them (L2) with the k2 / v2 rows, one 64-channel block at
+// a time, so that the thread holds 128 registers of operands in both cases.
+template <int D>
 __device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, uint8_t *sA, uint8_t *sB,
                                           uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
@@ -110,78 +150,132 @@ __device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, ui
     const bool iv = i < kp.n;
     const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
     const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p);
-    uint4 qv[8], dv[8];
+    const __nv_bfloat16 *qp = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, iv ? i : 0, h);
+    const __nv_bfloat16 *dp = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, iv ? i : 0, h);
+    const int nv = g.nsweeps;
+    if constexpr (D == 64) {
+        uint4 qv[8], dv[8];
 #pragma unroll
-    for (int cc = 0; cc < 8; ++cc) { qv[cc] = make_uint4(0, 0, 0, 0); dv[cc] = make_uint4(0, 0, 0, 0); }
-    if (iv) {
-        const __nv_bfloat16 *qp = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, i, h);
-        const __nv_bfloat16 *dp = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, i, h);
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-            qv[cc] = *reinterpret_cast<const uint4 *>(qp + cc * 8);
-            dv[cc] = *reinterpret_cast<const uint4 *>(dp + cc * 8);
-        }
-    }
-    for (int e = 0; e < g.nsweeps; ++e) {
-        // fetch the second-key rows before waiting, so their latency overlaps the previous sweep
-        const int kk = i + kp.off2 - e;
-        const bool ok = iv && kk >= 0;
-        uint4 kv[8], vv[8];
-        if (ok) {
-            const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, kk, hk);
-            const __nv_bfloat16 *vp2 = v2 + elem_off(kp.v2, b, kk, hk);
+        for (int cc = 0; cc < 8; ++cc) { qv[cc] = make_uint4(0, 0, 0, 0); dv[cc] = make_uint4(0, 0, 0, 0); }
+        if (iv) {
 #pragma unroll
             for (int cc = 0; cc < 8; ++cc) {
-                kv[cc] = *reinterpret_cast<const uint4 *>(kp2 + cc * 8);
-                vv[cc] = *reinterpret_cast<const uint4 *>(vp2 + cc * 8);
+                qv[cc] = *reinterpret_cast<const uint4 *>(qp + cc * 8);
+                dv[cc] = *reinterpret_cast<const uint4 *>(dp + cc * 8);
             }
         }
-        if (e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag)) return ERR_BQ_BUILDER;
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-            uint4 a = make_uint4(0, 0, 0, 0), bb = make_uint4(0, 0, 0, 0);
+        for (int v = 0; v < nv; ++v) {
+            const int e = v;
+            // fetch the second-key rows before waiting, so their latency overlaps the previous sweep
+            const int kk = i + kp.off2 - e;
+            const bool ok = iv && kk >= 0;
+            uint4 kv[8], vv[8];
             if (ok) {
-                a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
-                a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
-                bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
-                bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
+                const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, kk, hk);
+                const __nv_bfloat16 *vp2 = v2 + elem_off(kp.v2, b, kk, hk);
+#pragma unroll
+                for (int cc = 0; cc < 8; ++cc) {
+                    kv[cc] = *reinterpret_cast<const uint4 *>(kp2 + cc * 8);
+                    vv[cc] = *reinterpret_cast<const uint4 *>(vp2 + cc * 8);
+                }
             }
-            *reinterpret_cast<uint4 *>(sA + sw128_offset(r, cc)) = a;
-            *reinterpret_cast<uint4 *>(sB + sw128_offset(r, cc)) = bb;
+            if (v >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (v - 1) & 1, abort_flag)) return ERR_BQ_BUILDER;
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                uint4 a = make_uint4(0, 0, 0, 0), bb = make_uint4(0, 0, 0, 0);
+                if (ok) {
+                    a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
+                    a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
+                    bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
+                    bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
+                }
+                *reinterpret_cast<uint4 *>(sA + sw128_offset(r, cc)) = a;
+                *reinterpret_cast<uint4 *>(sB + sw128_offset(r, cc)) = bb;
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&bars[BQ_AB_FULL]);
         }
-        fence_proxy_async_smem();
-        mbar_arrive(&bars[BQ_AB_FULL]);
+    } else {
+        for (int v = 0; v < nv; ++v) {
+            const int e = v;
+            const int kk = i + kp.off2 - e;
+            const bool ok = iv && kk >= 0;
+            const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+            const __nv_bfloat16 *vp2 = v2 + elem_off(kp.v2, b, ok ? kk : 0, hk);
+#pragma unroll
+            for (int cb = 0; cb < 2; ++cb) {
+                uint4 qv[8], dv[8], kv[8], vv[8];
+#pragma unroll
+                for (int cc = 0; cc < 8; ++cc) {
+                    const int c8 = cb * 64 + cc * 8;
+                    if (ok) {
+                        qv[cc] = __ldg(reinterpret_cast<const uint4 *>(qp + c8));
+                        dv[cc] = __ldg(reinterpret_cast<const uint4 *>(dp + c8));
+                        kv[cc] = __ldg(reinterpret_cast<const uint4 *>(kp2 + c8));
+                        vv[cc] = __ldg(reinterpret_cast<const uint4 *>(vp2 + c8));
+                    } else {
+                        qv[cc] = dv[cc] = kv[cc] = vv[cc] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+                // the loads of the first block are in flight while the previous sweep still reads the stage
+                if (cb == 0 && v >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (v - 1) & 1, abort_flag)) return ERR_BQ_BUILDER;
+#pragma unroll
+                for (int cc = 0; cc < 8; ++cc) {
+                    uint4 a, bb;
+                    a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
+                    a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
+                    bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
+                    bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
+                    *reinterpret_cast<uint4 *>(sA + cb * BqCfg<D>::BLK + sw128_offset(r, cc)) = a;
+                    *reinterpret_cast<uint4 *>(sB + cb * BqCfg<D>::BLK + sw128_offset(r, cc)) = bb;
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&bars[BQ_AB_FULL]);
+        }
     }
     return 0;
 }
 
-// ---------------------------------------------------------------- issuer of S, dP (warp 1, one lane)
-// Unit u = e * upe + within covers keys [64 (within & 1), +64) of tile within >> 1 of the split; units
-// alternate between the two halves, so half == u & 1.  One thread issues about one tcgen05.mma per 90
-// cycles, so the two product stages have an issuing thread each; U / W are accumulated by one thread
-// only, which keeps the summation order fixed.
-// which = 0: S = A_e K1^T into columns [128 half, +64) (warp 1); which = 1: dP = B_e V1^T into
-// [128 half + 64, +64) (warp 2).  A thread each: the time from "U / W of the half's previous unit are done"
-// to "the next S / dP are complete" is on the critical chain of every unit.
+// ---------------------------------------------------------------- issuers of S (warp 1) and dP (warp 2), one lane each
+// Unit u (numbered over the whole kernel) is unit u % nunits of sweep u / nunits and uses TMEM half u & 1.
+// One thread issues about one tcgen05.mma per 60-90 cycles, so the two product stages have an issuing
+// thread each; U / W are accumulated by one thread only, which keeps the summation order fixed.
+// which = 0: S = A_e K1^T into columns [128 half, +64); which = 1: dP = B_e V1^T into [128 half + 64, +64).
+template <int D>
 __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t tmem, uint8_t *sKV, uint8_t *sAB,
                                             uint64_t *bars, volatile int *abort_flag) {
+    using C = BqCfg<D>;
     constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);
     const uint64_t dT = smem_desc_sw128(smem_u32(sKV)), dA = smem_desc_sw128(smem_u32(sAB));
-    if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_MMA;
+    if constexpr (D == 64) {
+        if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_MMA;
+    }
     int u = 0;
     for (int e = 0; e < g.nsweeps; ++e) {
         if (!mbar_wait(&bars[BQ_AB_FULL], e & 1, abort_flag)) return ERR_BQ_MMA;
-        for (int within = 0; within < g.upe; ++within, ++u) {
-            const int half = within & 1;
-            // the buffer holds P / G of this half's previous unit until its U / W products are done
-            if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
+        for (int w = 0; w < g.nunits; ++w, ++u) {
+            const int half = u & 1;
+            if constexpr (D == 64) {
+                // the buffer holds P / G of this half's previous unit until its U / W products are done
+                if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
+            } else {
+                // the unit lands in slot `half` after the U / W products of the slot's previous unit are done
+                if (!mbar_wait(&bars[BQ_KV_SLOT + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_MMA;
+            }
             tc_fence_after();
-            const uint64_t t = dT + (uint64_t)(((within >> 1) * TILE_BYTES + half * 8192) >> 4);
             const uint32_t d = tmem + half * 128 + which * 64;
-            mma_ss(d, dA, t, IDESC_F, 0u);
-            mma_ss(d, dA + 2, t + 2, IDESC_F, 1u);
-            mma_ss(d, dA + 4, t + 4, IDESC_F, 1u);
-            mma_ss(d, dA + 6, t + 6, IDESC_F, 1u);
+            if constexpr (D == 64) {
+                const uint64_t t = dT + (uint64_t)((w * 8192) >> 4);       // unit w: rows [64 w, +64) of the resident tiles
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mma_ss(d, dA + 2 * k, t + 2 * k, IDESC_F, k > 0 ? 1u : 0u);
+            } else {
+                const uint64_t t = dT + (uint64_t)((half * 2 * C::UBLK) >> 4);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    mma_ss(d, dA + (uint64_t)(((k >> 2) * C::BLK) >> 4) + (uint64_t)((k & 3) * 2),
+                           t + (uint64_t)(((k >> 2) * C::UBLK) >> 4) + (uint64_t)((k & 3) * 2), IDESC_F, k > 0 ? 1u : 0u);
+            }
             tc_commit(&bars[BQ_S_FULL + half]);
         }
         tc_commit(&bars[BQ_AB_EMPTY]);
@@ -189,23 +283,67 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t
     return 0;
 }
 
-// ---------------------------------------------------------------- issuer of U, W (warp 0, one lane)
-__device__ __forceinline__ int bq_mma_second(const BqGeom &g, uint32_t tmem, uint8_t *sK, uint8_t *sV,
-                                             uint64_t *bars, volatile int *abort_flag) {
+// ---------------------------------------------------------------- head dim 128: TMA producer of the K1/V1 ring (warp 3, one lane)
+template <int D>
+__device__ __forceinline__ int bq_ring_producer(const BqParams &P, const BqGeom &g, const CUtensorMap *mapK, const CUtensorMap *mapV,
+                                                uint8_t *sK, uint8_t *sV, uint64_t *bars, volatile int *abort_flag) {
+    using C = BqCfg<D>;
+    const int hk = blockIdx.y / P.kp.g;
+    prefetch_tmap(mapK);
+    prefetch_tmap(mapV);
+    int w = 0;
+    for (int u = 0; u < g.total; ++u) {
+        const int half = u & 1;
+        if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag, 32)) return ERR_BQ_PRODUCER;
+        const int row = g.ubase + 64 * w;
+        mbar_arrive_expect_tx(&bars[BQ_KV_SLOT + half], 4 * C::UBLK);
+#pragma unroll
+        for (int cb = 0; cb < 2; ++cb) {
+            tma_load_4d(sK + half * 2 * C::UBLK + cb * C::UBLK, mapK, &bars[BQ_KV_SLOT + half], cb * 64, hk, row, blockIdx.z);
+            tma_load_4d(sV + half * 2 * C::UBLK + cb * C::UBLK, mapV, &bars[BQ_KV_SLOT + half], cb * 64, hk, row, blockIdx.z);
+        }
+        if (++w == g.nunits) w = 0;
+    }
+    // every load must have landed before the CTA may exit, even if the consumers gave up
+    for (int u = max(0, g.total - 2); u < g.total; ++u)
+        if (!mbar_wait(&bars[BQ_KV_SLOT + (u & 1)], (u >> 1) & 1, abort_flag, 32)) return ERR_BQ_PRODUCER;
+    return 0;
+}
+
+// ---------------------------------------------------------------- issuer of U, W (warp 0, one lane; head dim 64: also loads the tiles)
+template <int D>
+__device__ __forceinline__ int bq_mma_second(const BqParams &P, const BqGeom &g, const CUtensorMap *mapK, const CUtensorMap *mapV,
+                                             uint32_t tmem, uint8_t *sK, uint8_t *sV, uint64_t *bars, volatile int *abort_flag) {
+    using C = BqCfg<D>;
     constexpr uint32_t IDESC_G = idesc_bf16(128, 64, false, true);
-    const uint64_t dK = smem_desc_sw128(smem_u32(sK)), dV = smem_desc_sw128(smem_u32(sV));
+    if constexpr (D == 64) {
+        const int hk = blockIdx.y / P.kp.g;
+        prefetch_tmap(mapK);
+        prefetch_tmap(mapV);
+        const int nt = g.nunits / 2;
+        mbar_arrive_expect_tx(&bars[BQ_KV_FULL], 2 * C::BLK * nt);
+        for (int t = 0; t < nt; ++t) {
+            const int row = g.ubase + TJ * t;
+            tma_load_4d(sK + (size_t)t * C::BLK, mapK, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+            tma_load_4d(sV + (size_t)t * C::BLK, mapV, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+        }
+        if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_PRODUCER;
+    }
+    // head dim 128: U / W take the CTA's 64-channel block of the unit as an MN-major B operand
+    const uint64_t dK = smem_desc_sw128(smem_u32(sK) + (D == 64 ? 0 : g.chh * C::UBLK));
+    const uint64_t dV = smem_desc_sw128(smem_u32(sV) + (D == 64 ? 0 : g.chh * C::UBLK));
     int u = 0;
     for (int e = 0; e < g.nsweeps; ++e) {
         const int wb = e & 1;
-        for (int within = 0; within < g.upe; ++within, ++u) {
-            const int half = within & 1;
+        for (int w = 0; w < g.nunits; ++w, ++u) {
+            const int half = u & 1;
             if (!mbar_wait(&bars[BQ_P_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_MMA;
-            if (within == 0 && e >= 2 && !mbar_wait(&bars[BQ_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
+            if (w == 0 && e >= 2 && !mbar_wait(&bars[BQ_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
             tc_fence_after();
-            const uint64_t off = (uint64_t)(((within >> 1) * TILE_BYTES + half * 8192) >> 4);
+            const uint64_t off = (uint64_t)((D == 64 ? w * 8192 : half * 2 * C::UBLK) >> 4);
             const uint64_t kt = dK + off, vt = dV + off;
             const uint32_t a = tmem + half * 128;
-            const uint32_t acc = within > 0 ? 1u : 0u;
+            const uint32_t acc = w > 0 ? 1u : 0u;
             mma_ts(tmem + 256 + wb * 128, a + 64, kt, IDESC_G, acc);           // U += G K1
             mma_ts(tmem + 256 + wb * 128, a + 72, kt + 128, IDESC_G, 1u);
             mma_ts(tmem + 256 + wb * 128, a + 80, kt + 256, IDESC_G, 1u);
@@ -222,6 +360,7 @@ __device__ __forceinline__ int bq_mma_second(const BqGeom &g, uint32_t tmem, uin
 }
 
 // ---------------------------------------------------------------- compute (warps 4-7): P and G
+template <int D>
 __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, uint32_t tmem, uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -237,54 +376,57 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
         lse2 = kp.lse[o] * 1.4426950408889634f;
         dl = kp.delta[o];
     }
-    for (int e = 0; e < g.nsweeps; ++e) {
-        const bool sweep_ok = row_ok && (i + kp.off2 - e >= 0);
-        for (int within = 0; within < g.upe; ++within) {
-            const int u = e * g.upe + within, jt = within >> 1, half = within & 1;
-            const int j0 = g.jbase + TJ * (g.t_begin + jt) + 64 * half;
-            const int d1 = i + kp.off1 - j0;
-            const int hi = sweep_ok ? min(d1, 63) : -1;         // valid columns: lo < col <= hi
-            const int lo = max(d1 - kp.w1, -j0 - 1);
-            if (!warp_wait(&bars[BQ_S_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_COMPUTE;
-            tc_fence_after();
-            const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
+    int u = 0;
+    {
+        for (int e = 0; e < g.nsweeps; ++e) {
+            const bool sweep_ok = row_ok && (i + kp.off2 - e >= 0);
+            for (int w = 0; w < g.nunits; ++w, ++u) {
+                const int half = u & 1;
+                const int j0 = g.ubase + 64 * w;
+                const int d1 = i + kp.off1 - j0;
+                const int hi = sweep_ok ? min(d1, 63) : -1;         // valid columns: lo < col <= hi
+                const int lo = max(d1 - kp.w1, -j0 - 1);
+                if (!warp_wait(&bars[BQ_S_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_COMPUTE;
+                tc_fence_after();
+                const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
 #pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t sv[32], dv[32], pp[16], gg[16];
-                tmem_ld32(lane_addr + half * 128 + ch * 32, sv);
-                tmem_ld32(lane_addr + half * 128 + 64 + ch * 32, dv);
-                tmem_wait_ld();
-                if (full) {
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t sv[32], dv[32], pp[16], gg[16];
+                    tmem_ld32(lane_addr + half * 128 + ch * 32, sv);
+                    tmem_ld32(lane_addr + half * 128 + 64 + ch * 32, dv);
+                    tmem_wait_ld();
+                    if (full) {
 #pragma unroll
-                    for (int x = 0; x < 32; x += 2) {
-                        const float p0 = ex2(fmaf(__uint_as_float(sv[x]), c, -lse2));
-                        const float p1 = ex2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
-                        pp[x >> 1] = pack_bf16(p0, p1);
-                        gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
+                        for (int x = 0; x < 32; x += 2) {
+                            const float p0 = ex2(fmaf(__uint_as_float(sv[x]), c, -lse2));
+                            const float p1 = ex2(fmaf(__uint_as_float(sv[x + 1]), c, -lse2));
+                            pp[x >> 1] = pack_bf16(p0, p1);
+                            gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
+                        }
+                    } else {
+                        // valid columns are the integers in (lo, hi]: saturate(half + 1 - |col - mid|) is exactly 1
+                        // inside and 0 outside (FMA pipe instead of compares and selects on the ALU pipe); the
+                        // exponent is clamped so that a masked-out cell cannot give inf * 0
+                        const float mid = 0.5f * (float)(lo + 1 + hi), hwp = 0.5f * (float)(hi - lo - 1) + 1.f;
+#pragma unroll
+                        for (int x = 0; x < 32; x += 2) {
+                            const int col = ch * 32 + x;
+                            const float v0 = __saturatef(hwp - fabsf((float)col - mid));
+                            const float v1 = __saturatef(hwp - fabsf((float)(col + 1) - mid));
+                            const float p0 = ex2(fminf(fmaf(__uint_as_float(sv[x]), c, -lse2), 100.f)) * v0;
+                            const float p1 = ex2(fminf(fmaf(__uint_as_float(sv[x + 1]), c, -lse2), 100.f)) * v1;
+                            pp[x >> 1] = pack_bf16(p0, p1);
+                            gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
+                        }
                     }
-                } else {
-                    // valid columns are the integers in (lo, hi]: saturate(half + 1 - |col - mid|) is exactly 1
-                    // inside and 0 outside (FMA pipe instead of compares and selects on the ALU pipe); the
-                    // exponent is clamped so that a masked-out cell cannot give inf * 0
-                    const float mid = 0.5f * (float)(lo + 1 + hi), hwp = 0.5f * (float)(hi - lo - 1) + 1.f;
-#pragma unroll
-                    for (int x = 0; x < 32; x += 2) {
-                        const int col = ch * 32 + x;
-                        const float v0 = __saturatef(hwp - fabsf((float)col - mid));
-                        const float v1 = __saturatef(hwp - fabsf((float)(col + 1) - mid));
-                        const float p0 = ex2(fminf(fmaf(__uint_as_float(sv[x]), c, -lse2), 100.f)) * v0;
-                        const float p1 = ex2(fminf(fmaf(__uint_as_float(sv[x + 1]), c, -lse2), 100.f)) * v1;
-                        pp[x >> 1] = pack_bf16(p0, p1);
-                        gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
-                    }
+                    // P / G chunk over columns of S / dP that have already been read
+                    tmem_st16(lane_addr + half * 128 + ch * 16, pp);
+                    tmem_st16(lane_addr + half * 128 + 64 + ch * 16, gg);
                 }
-                // P / G chunk over columns of S / dP that have already been read
-                tmem_st16(lane_addr + half * 128 + ch * 16, pp);
-                tmem_st16(lane_addr + half * 128 + 64 + ch * 16, gg);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&bars[BQ_P_FULL + half]);
             }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&bars[BQ_P_FULL + half]);
         }
     }
     return 0;
@@ -293,6 +435,7 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
 // ---------------------------------------------------------------- fold (warps 8-11): U, W -> dQ, dK2, dV2
 __device__ __forceinline__ void bq_fold_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+template <int D>
 __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
                                             uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
@@ -300,19 +443,19 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
     const int r = (warp & 3) * 32 + lane;             // query row within the tile = TMEM lane
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
-    const int split = blockIdx.x % P.nsplit;
+    const int c0 = g.chh * 64;                        // first channel this CTA produces
     const int i = g.i0 + r;
     const bool row_ok = i < kp.n;
     float dq[64];
 #pragma unroll
     for (int x = 0; x < 64; ++x) dq[x] = 0.f;
-    const __nv_bfloat16 *qrow = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, row_ok ? i : 0, h);
-    const __nv_bfloat16 *dorow = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, row_ok ? i : 0, h);
-    const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
+    const __nv_bfloat16 *qrow = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, row_ok ? i : 0, h) + c0;
+    const __nv_bfloat16 *dorow = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, row_ok ? i : 0, h) + c0;
+    const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p) + c0;
 
-    auto drain = [&](int e) -> bool {
-        const int wb = e & 1;
-        if (!warp_wait(&bars[BQ_W_FULL + wb], (e >> 1) & 1, abort_flag)) return false;
+    auto drain = [&](int v) -> bool {
+        const int wb = v & 1, e = v;
+        if (!warp_wait(&bars[BQ_W_FULL + wb], (v >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
         const int kk = i + kp.off2 - e;
         const bool ok = row_ok && kk >= 0;
@@ -377,56 +520,63 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
         return true;
     };
 
-    if (g.total > 0)
-        for (int e = 0; e < g.nsweeps; ++e) {
-            if (!drain(e)) return ERR_BQ_COMPUTE;
-            // Row i-e of the shared accumulators is written by thread r in this sweep and by thread r+1 in
-            // the next: every fold thread must have finished sweep e (all have arrived on W_EMPTY) first.
-            if (!warp_wait(&bars[BQ_W_EMPTY + (e & 1)], (e >> 1) & 1, abort_flag)) return ERR_BQ_COMPUTE;
-        }
+    const int nv = g.total > 0 ? g.nsweeps : 0;       // a split whose tiles all lie before the sequence start has no work
+    int err = 0;
+    for (int v = 0; v < nv && err == 0; ++v) {
+        if (!drain(v)) err = ERR_BQ_COMPUTE;
+        // A row of the shared accumulators is written by thread r in this sweep and by another thread in
+        // the next: every fold thread must have finished this one (all have arrived on W_EMPTY) first.
+        else if (!warp_wait(&bars[BQ_W_EMPTY + (v & 1)], (v >> 1) & 1, abort_flag)) err = ERR_BQ_COMPUTE;
+    }
 
-    // partial dQ of this split
+    // partial dQ of this split (NaN when a wait ran out, so that the failure is visible in the result)
     if (row_ok) {
-        float *dst = P.part_dq + ((((size_t)split * kp.b + b) * kp.n + i) * kp.hq + h) * 64;
+        const bool bad = err != 0 || *abort_flag != 0;
+        float *dst = P.part_dq + ((((size_t)g.split * kp.b + b) * kp.n + i) * kp.hq + h) * D + c0;
 #pragma unroll
         for (int x = 0; x < 64; x += 4)
-            *reinterpret_cast<float4 *>(dst + x) = make_float4(dq[x], dq[x + 1], dq[x + 2], dq[x + 3]);
+            *reinterpret_cast<float4 *>(dst + x) = bad ? make_float4(CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F)
+                                                       : make_float4(dq[x], dq[x + 1], dq[x + 2], dq[x + 3]);
     }
-    return 0;
+    return err;
 }
 
+template <int D>
 __device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
                                        uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int ft = threadIdx.x - 256;                 // 0..127 among the fold threads
     const int h = blockIdx.y, b = blockIdx.z;
-    const int qt = blockIdx.x / P.nsplit, split = blockIdx.x % P.nsplit;
     const int acc_rows = 127 + kp.w2;
     // zero the shared accumulators (acc_v follows acc_k); only this group touches them
     for (int x = ft; x < 2 * acc_rows * BQ_ACC_STRIDE; x += 128) acc_k[x] = 0.f;
     bq_fold_sync();
-    const int err = bq_fold_body(P, g, tmem, acc_k, acc_v, bars, abort_flag);
-    // shared accumulators -> this CTA's slab.  The barrier sits outside the body so that a warp
-    // that gave up on a wait still reaches it.
+    const int err = bq_fold_body<D>(P, g, tmem, acc_k, acc_v, bars, abort_flag);
+    // shared accumulators -> this CTA's 64 channels of its slab.  The barrier sits outside the body so
+    // that a warp that gave up on a wait still reaches it.
     bq_fold_sync();
-    float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + qt) * P.nsplit + split) * (size_t)(2 * acc_rows * 64);
+    float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + g.qt) * P.nsplit + g.split) * (size_t)(2 * acc_rows * D) + g.chh * 64;
+    const bool bad = err != 0 || *abort_flag != 0;     // a CTA in which a wait ran out reports NaN
     for (int x = ft; x < 2 * acc_rows * 16; x += 128) {
         const int row = x >> 4, c4 = (x & 15) * 4;      // row over both arrays
-        const float4 v = *reinterpret_cast<const float4 *>(acc_k + (size_t)row * BQ_ACC_STRIDE + c4);
-        *reinterpret_cast<float4 *>(slab + (size_t)row * 64 + c4) = v;
+        float4 v = *reinterpret_cast<const float4 *>(acc_k + (size_t)row * BQ_ACC_STRIDE + c4);
+        if (bad) v = make_float4(CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F);
+        *reinterpret_cast<float4 *>(slab + (size_t)row * D + c4) = v;
     }
     return err;
 }
 
+template <int D>
 __global__ void __launch_bounds__(BQ_THREADS, 1)
 bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, const BqParams P) {
+    using C = BqCfg<D>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sK = smem;
-    uint8_t *sV = sK + BQ_MAX_TILES * TILE_BYTES;
-    uint8_t *sA = sV + BQ_MAX_TILES * TILE_BYTES;
-    uint8_t *sB = sA + TILE_BYTES;
-    float *acc_k = reinterpret_cast<float *>(sB + TILE_BYTES);
+    uint8_t *sV = sK + C::KV_BYTES;
+    uint8_t *sA = sV + C::KV_BYTES;
+    uint8_t *sB = sA + C::TILE;
+    float *acc_k = reinterpret_cast<float *>(sB + C::TILE);
     const int acc_rows = 127 + P.kp.w2;
     float *acc_v = acc_k + (size_t)acc_rows * BQ_ACC_STRIDE;
     uint64_t *bars = reinterpret_cast<uint64_t *>(acc_v + (size_t)acc_rows * BQ_ACC_STRIDE);
@@ -452,40 +602,31 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_holder;
-    const BqGeom g = bq_geom(P);
+    const BqGeom g = bq_geom<D>(P);
 
     int err = 0;
     if (warp < 4) {
         reg_dealloc<BQ_REGS_ISSUE>();                 // one instruction for the whole warpgroup
         if (warp == 0) {
-            if (lane == 0 && g.total > 0) {
-                const int hk = blockIdx.y / P.kp.g;
-                prefetch_tmap(&mapK);
-                prefetch_tmap(&mapV);
-                mbar_arrive_expect_tx(&bars[BQ_KV_FULL], 2 * TILE_BYTES * g.ntl);
-                for (int t = 0; t < g.ntl; ++t) {
-                    const int row = g.jbase + TJ * (g.t_begin + t);
-                    tma_load_4d(sK + (size_t)t * TILE_BYTES, &mapK, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
-                    tma_load_4d(sV + (size_t)t * TILE_BYTES, &mapV, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
-                }
-                if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) err = ERR_BQ_PRODUCER;
-                else err = bq_mma_second(g, tmem, sK, sV, bars, abort_flag);
-            }
+            if (lane == 0 && g.total > 0) err = bq_mma_second<D>(P, g, &mapK, &mapV, tmem, sK, sV, bars, abort_flag);
             __syncwarp();
         } else if (warp == 1 || warp == 2) {
             if (lane == 0 && g.total > 0)
-                err = bq_mma_first(g, warp - 1, tmem, warp == 1 ? sK : sV, warp == 1 ? sA : sB, bars, abort_flag);
+                err = bq_mma_first<D>(g, warp - 1, tmem, warp == 1 ? sK : sV, warp == 1 ? sA : sB, bars, abort_flag);
+            __syncwarp();
+        } else if constexpr (D == 128) {
+            if (lane == 0 && g.total > 0) err = bq_ring_producer<D>(P, g, &mapK, &mapV, sK, sV, bars, abort_flag);
             __syncwarp();
         }
     } else if (warp < 8) {
         reg_dealloc<BQ_REGS_COMPUTE>();
-        err = bq_compute(P, g, tmem, bars, abort_flag);
+        err = bq_compute<D>(P, g, tmem, bars, abort_flag);
     } else if (warp < 12) {
         reg_alloc<BQ_REGS_FOLD>();
-        err = bq_fold(P, g, tmem, acc_k, acc_v, bars, abort_flag);
+        err = bq_fold<D>(P, g, tmem, acc_k, acc_v, bars, abort_flag);
     } else {
         reg_alloc<BQ_REGS_BUILD>();
-        if (g.total > 0) err = bq_builder(P, g, sA, sB, bars, abort_flag);
+        if (g.total > 0) err = bq_builder<D>(P, g, sA, sB, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
 
@@ -506,22 +647,24 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
 // T at slab row k - off2 - 128 T + (w2 - 1), for the one or two tiles where
 // that index falls inside [0, 127 + w2).
 // ---------------------------------------------------------------------------
+template <int D>
 __global__ void bwd_q_reduce_kernel(const BqParams P) {
+    constexpr int TPR = D / 4;                          // threads per row
     const KernelParams &kp = P.kp;
     const int acc_rows = 127 + kp.w2;
-    const int64_t nq = (int64_t)kp.b * kp.n * kp.hq * 16;
-    const int64_t nk = (int64_t)kp.b * kp.nk2 * kp.hk * 16;
+    const int64_t nq = (int64_t)kp.b * kp.n * kp.hq * TPR;
+    const int64_t nk = (int64_t)kp.b * kp.nk2 * kp.hk * TPR;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const bool gbf16 = kp.grad_bf16 != 0;
     if (idx < nq) {
-        const int c4 = (int)(idx & 15) * 4;
-        int64_t rest = idx >> 4;
+        const int c4 = (int)(idx % TPR) * 4;
+        int64_t rest = idx / TPR;
         const int h = (int)(rest % kp.hq); rest /= kp.hq;
         const int i = (int)(rest % kp.n);
         const int b = (int)(rest / kp.n);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int s = 0; s < P.nsplit; ++s) {
-            const float4 v = *reinterpret_cast<const float4 *>(P.part_dq + ((((size_t)s * kp.b + b) * kp.n + i) * kp.hq + h) * 64 + c4);
+            const float4 v = *reinterpret_cast<const float4 *>(P.part_dq + ((((size_t)s * kp.b + b) * kp.n + i) * kp.hq + h) * D + c4);
             acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
         }
 #pragma unroll
@@ -529,8 +672,8 @@ __global__ void bwd_q_reduce_kernel(const BqParams P) {
         store_vec<4>(kp.dq.p, elem_off(kp.dq, b, i, h) + c4, gbf16, acc);
     } else if (idx < nq + nk) {
         const int64_t id2 = idx - nq;
-        const int c4 = (int)(id2 & 15) * 4;
-        int64_t rest = id2 >> 4;
+        const int c4 = (int)(id2 % TPR) * 4;
+        int64_t rest = id2 / TPR;
         const int hk = (int)(rest % kp.hk); rest /= kp.hk;
         const int k = (int)(rest % kp.nk2);
         const int b = (int)(rest / kp.nk2);
@@ -544,9 +687,9 @@ __global__ void bwd_q_reduce_kernel(const BqParams P) {
                 const int row = pos - TQ * T + kp.w2 - 1;
                 if (row < 0 || row >= acc_rows) continue;
                 for (int s = 0; s < P.nsplit; ++s) {
-                    const float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + T) * P.nsplit + s) * (size_t)(2 * acc_rows * 64);
-                    const float4 vk = *reinterpret_cast<const float4 *>(slab + (size_t)row * 64 + c4);
-                    const float4 vv = *reinterpret_cast<const float4 *>(slab + (size_t)(acc_rows + row) * 64 + c4);
+                    const float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + T) * P.nsplit + s) * (size_t)(2 * acc_rows * D);
+                    const float4 vk = *reinterpret_cast<const float4 *>(slab + (size_t)row * D + c4);
+                    const float4 vv = *reinterpret_cast<const float4 *>(slab + (size_t)(acc_rows + row) * D + c4);
                     ak[0] += vk.x; ak[1] += vk.y; ak[2] += vk.z; ak[3] += vk.w;
                     av[0] += vv.x; av[1] += vv.y; av[2] += vv.z; av[3] += vv.w;
                 }

@@ -101,17 +101,6 @@ inline size_t fwd_smem_bytes(int nt) {
     return need > 120 * 1024 ? need : 120 * 1024;
 }
 
-// Optional timeline of one CTA (compile with -DSA2_TRACE): clock64 stamps at the pipeline's hand-over points.
-#ifdef SA2_TRACE
-__device__ unsigned long long g_trace[8192];
-__device__ __forceinline__ void trace_mark(int slot) {
-    if (blockIdx.x == 20 && blockIdx.y == 0 && blockIdx.z == 0 && slot < 8192) g_trace[slot] = clock64();
-}
-#define SA2_TRACE_MARK(cond, slot) do { if (cond) trace_mark(slot); } while (0)
-#else
-#define SA2_TRACE_MARK(cond, slot) do { } while (0)
-#endif
-
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -216,9 +205,7 @@ __device__ __forceinline__ int fwd_mma(const FwdGeom &g, int grp, uint32_t tmem,
     };
     auto issue_pv = [&](int r) -> bool {
         const int tile = g.t_first + (p_w >> 1), half = p_w & 1, sb = r & 1;
-        SA2_TRACE_MARK(true, 4096 + (grp * 160 + r) * 4);
         if (!mbar_wait(&bars[BAR_P_FULL + grp * 2 + sb], (r >> 1) & 1, abort_flag)) return false;
-        SA2_TRACE_MARK(true, 4096 + (grp * 160 + r) * 4 + 1);
         if (p_w == 0 && p_k >= 1 && !mbar_wait(&bars[BAR_W_EMPTY + grp], (p_k - 1) & 1, abort_flag)) return false;
         tc_fence_after();
         const uint64_t vt = dV + (uint64_t)((tile * TILE_BYTES + half * 8192) >> 4);
@@ -229,7 +216,6 @@ __device__ __forceinline__ int fwd_mma(const FwdGeom &g, int grp, uint32_t tmem,
         mma_ts(tW, a + 24, vt + 384, IDESC_PV, 1u);
         tc_commit(&bars[BAR_PV_DONE + grp * 2 + sb]);
         if (p_w == g.upe - 1) tc_commit(&bars[BAR_W_FULL + grp]);
-        SA2_TRACE_MARK(true, 4096 + (grp * 160 + r) * 4 + 2);
         if (++p_w == g.upe) { p_w = 0; ++p_k; }
         return true;
     };
@@ -303,9 +289,7 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             const int d1 = i + kp.off1 - j0;
             const int hi = sweep_ok ? min(d1, 63) : -1;
             const int lo = max(d1 - kp.w1, -j0 - 1);
-            SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4);
             if (!warp_wait(&bars[BAR_S_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
-            SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 1);
             tc_fence_after();
             const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
 
@@ -367,7 +351,6 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             }
             l += tile_sum;
             tmem_wait_st();
-            SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 2);
             if (w == g.upe - 1) {
                 // W_e is expressed against the reference the row has now.  The output thread has read the
                 // slot of sweep k - 2 before it released that sweep's W; waiting for the release of sweep
@@ -378,7 +361,6 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             }
             tc_fence_before();
             mbar_arrive(&bars[BAR_P_FULL + grp * 2 + sb]);
-            SA2_TRACE_MARK(r == 0, grp * 2048 + u * 4 + 3);
         }
     }
     stats[512 + grp * 128 + r] = l;
@@ -415,7 +397,6 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
 
     // row r of A_e = q_i * k2_{i-e} for sweep e = 2 k + grp, into the group's A stage
     auto build_a = [&](int grp, int k) {
-        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8);
         const int e = 2 * k + grp;
         uint8_t *dst = sA + (size_t)grp * TILE_BYTES;
         const int kk = i + kp.off2 - e;
@@ -435,20 +416,15 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
             v.z = mul_bf16x2(qv[cc].z, kv[cc].z); v.w = mul_bf16x2(qv[cc].w, kv[cc].w);
             *reinterpret_cast<uint4 *>(dst + sw128_offset(r, cc)) = v;
         }
-        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 7);
         fence_proxy_async_smem();
         mbar_arrive(&bars[BAR_A_FULL + grp]);
-        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 1);
     };
 
     // o += v2_{i-e} * W_e (TMEM), after moving o to the reference W_e was built against
     auto drain = [&](int grp, int k, float (&o)[64], float &ref_o) -> bool {
-        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 2);
         if (!warp_wait(&bars[BAR_REF_FULL + grp], k & 1, abort_flag)) return false;
-        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 3);
         const float ref_w = stats[grp * 256 + (k & 1) * 128 + r];
         if (!warp_wait(&bars[BAR_W_FULL + grp], k & 1, abort_flag)) return false;
-        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 4);
         tc_fence_after();
         const int kk = i + kp.off2 - (2 * k + grp);
         const bool ok = row_ok && kk >= 0 && ref_w > -CUDART_INF_F;
@@ -483,7 +459,6 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
         }
         tc_fence_before();
         mbar_arrive(&bars[BAR_W_EMPTY + grp]);
-        SA2_TRACE_MARK(r == 0, 6000 + (k * 2 + grp) * 8 + 5);
         return true;
     };
 
@@ -493,12 +468,10 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
     for (int k = 0; k < nsw0; ++k) {
         // the A stages first: the tensor cores wait for them, the W accumulators have a unit's slack
         if (k + 1 < nsw0) {
-            SA2_TRACE_MARK(r == 0, 6000 + ((k + 1) * 2 + 0) * 8 + 6);
             if (!warp_wait(&bars[BAR_A_FREE + 0], k & 1, abort_flag)) return ERR_FWD_OUTPUT;
             build_a(0, k + 1);
         }
         if (k + 1 < nsw1) {
-            SA2_TRACE_MARK(r == 0, 6000 + ((k + 1) * 2 + 1) * 8 + 6);
             if (!warp_wait(&bars[BAR_A_FREE + 1], k & 1, abort_flag)) return ERR_FWD_OUTPUT;
             build_a(1, k + 1);
         }
@@ -580,11 +553,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
         const float f0 = lref0 > -CUDART_INF_F ? ex2(lref0 - rmax) : 0.f;
         const float f1 = lref1 > -CUDART_INF_F ? ex2(lref1 - rmax) : 0.f;
         const float l = l0 * f0 + l1 * f1;
-        if (i < kp.n && err == 0) {
+        if (i < kp.n) {
+            // a CTA in which any wait ran out reports NaN instead of leaving its rows unwritten
+            const bool bad = err != 0 || *abort_flag != 0;
             // an accumulator that last saw an older reference than its group's final one is moved to it
-            const float inv = 1.f / l;
-            const float s0 = ref0 > -CUDART_INF_F ? ex2(ref0 - rmax) * inv : 0.f;
-            const float s1 = ref1 > -CUDART_INF_F ? ex2(ref1 - rmax) * inv : 0.f;
+            const float inv = bad ? CUDART_NAN_F : 1.f / l;
+            const float s0 = ref0 > -CUDART_INF_F ? ex2(ref0 - rmax) * inv : (bad ? inv : 0.f);
+            const float s1 = ref1 > -CUDART_INF_F ? ex2(ref1 - rmax) * inv : (bad ? inv : 0.f);
             __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(kp.out.p) + elem_off(kp.out, blockIdx.z, i, blockIdx.y);
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -595,7 +570,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
                 v.w = pack_bf16(o0[u * 8 + 6] * s0 + o1[u * 8 + 6] * s1, o0[u * 8 + 7] * s0 + o1[u * 8 + 7] * s1);
                 *reinterpret_cast<uint4 *>(op + u * 8) = v;
             }
-            kp.lse[((int64_t)blockIdx.z * kp.hq + blockIdx.y) * kp.n + i] = (rmax + lg2(l)) * 0.6931471805599453f;
+            kp.lse[((int64_t)blockIdx.z * kp.hq + blockIdx.y) * kp.n + i] = bad ? CUDART_NAN_F : (rmax + lg2(l)) * 0.6931471805599453f;
         }
     }
     if (err) atomicOr(P.status, err);

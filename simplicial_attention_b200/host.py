@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import torch
 
-from .attention import sa2_backward, sa2_forward
+from .attention import check_device, sa2_backward, sa2_forward
 
 
 class HostPipeline:
@@ -35,6 +35,25 @@ class HostPipeline:
         self.slots = [None] * slots          # device copies of one chunk's six inputs
         self.free = [None] * slots           # event: the slot's inputs are no longer read
         self.turn = 0
+        self.timed = False                   # record_copies(): events around every chunk's copies
+        self._copies = []                    # (direction, bytes, start event, end event)
+
+    def record_copies(self, on=True):
+        """Time every chunk's host->device and device->host copies with events on the copy streams;
+        ``copy_stats()`` turns them into GB/s per direction (the time each copy stream was busy)."""
+        self.timed = bool(on)
+        self._copies = []
+
+    def copy_stats(self):
+        """``{"h2d_gbs", "d2h_gbs", "h2d_bytes", "d2h_bytes"}`` over the copies recorded since
+        ``record_copies()``; call after ``synchronize()``."""
+        res = {}
+        for name in ("h2d", "d2h"):
+            rows = [(nb, a.elapsed_time(b)) for d, nb, a, b in self._copies if d == name]
+            nbytes, ms = sum(r[0] for r in rows), sum(r[1] for r in rows)
+            res[name + "_bytes"] = nbytes
+            res[name + "_gbs"] = nbytes / (ms * 1e-3) / 1e9 if ms > 0 else None
+        return res
 
     def _stage(self, slot, parts):
         bufs = self.slots[slot]
@@ -56,10 +75,15 @@ class HostPipeline:
                 if self.free[slot] is not None:
                     self.s_in.wait_event(self.free[slot])
                 dev = self._stage(slot, parts)
+                if self.timed:
+                    t0 = torch.cuda.Event(enable_timing=True)
+                    t0.record(self.s_in)
                 for d_, p_ in zip(dev, parts):
                     d_.copy_(p_, non_blocking=True)
-                ready = torch.cuda.Event()
+                ready = torch.cuda.Event(enable_timing=self.timed)
                 ready.record(self.s_in)
+                if self.timed:
+                    self._copies.append(("h2d", sum(p_.numel() * p_.element_size() for p_ in parts), t0, ready))
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(ready)
                 q, k1, k2, v1, v2, dout = dev
@@ -70,9 +94,16 @@ class HostPipeline:
                 self.free[slot] = done
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(done)
+                if self.timed:
+                    t0 = torch.cuda.Event(enable_timing=True)
+                    t0.record(self.s_out)
                 for h_, d_ in zip(outputs, (out, *grads)):
                     h_[sl].copy_(d_, non_blocking=True)
                     d_.record_stream(self.s_out)
+                if self.timed:
+                    t1 = torch.cuda.Event(enable_timing=True)
+                    t1.record(self.s_out)
+                    self._copies.append(("d2h", sum(d_.numel() * d_.element_size() for d_ in (out, *grads)), t0, t1))
 
     def join(self):
         """Make the caller's current stream wait for everything queued so far."""
@@ -80,6 +111,9 @@ class HostPipeline:
         end.record(self.s_out)
         torch.cuda.current_stream(self.device).wait_event(end)
 
-    def synchronize(self):
-        """Block the host until every queued call has delivered its results."""
+    def synchronize(self, check=True):
+        """Block the host until every queued call has delivered its results, then (``check``) raise
+        ``Sa2Error`` if any kernel gave up on a bounded wait - its rows would hold NaN."""
         self.s_out.synchronize()
+        if check:
+            check_device()

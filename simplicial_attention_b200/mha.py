@@ -92,6 +92,9 @@ class HigherOrderAttention(Module):
     # One kernel normalises the whole fused projection instead of five RMSNorm modules plus casts
     # (CUDA tensors only; set to False to run the norms as separate torch modules, as the reference does).
     fused_head_norm = True
+    # The backward of that kernel keeps one fp32 partial row of the gain gradient per warp in shared
+    # memory (8 warps x channels x 4 bytes <= 200 KB); wider projections use the separate modules.
+    fused_head_norm_max_channels = 6400
 
     def _fused_norm(self, proj):
         """Per-head RMSNorm of the packed projection with the gains of q_norm / k_norms / v_norms tiled to
@@ -115,6 +118,7 @@ class HigherOrderAttention(Module):
         proj = self.to_qkv(tokens)
         fused = (self.fused_head_norm and self.qk_rmsnorm and proj.is_cuda and not self.head_first_dim
                  and self.dim_head_values == self.dim_head and self.dim_head in (32, 64, 128)
+                 and proj.shape[-1] <= self.fused_head_norm_max_channels
                  and proj.dtype in (torch.float32, torch.bfloat16))
         if fused:
             q, k, v = self._fused_norm(proj).split(self.split_dims, dim=-1)
@@ -150,6 +154,14 @@ class SlidingWindowTwoSimplicialMHA(HigherOrderAttention):
     def __init__(self, *args, w1=512, w2=32, **kwargs):
         assert "number_key_value_sets" not in kwargs
         assert "head_first_dim" not in kwargs
+        # the kernels contract q, k, k' and aggregate v, v' over one head dimension; say so at construction
+        # instead of failing at the first forward (the reference accepts the argument, simplicial_mha.py:34,
+        # and then fails inside its kernels, which read values with the key head dim)
+        dim_head = kwargs.get("dim_head", args[2] if len(args) > 2 else 64)
+        dim_head_values = kwargs.get("dim_head_values", args[3] if len(args) > 3 else None)
+        if dim_head_values is not None and dim_head_values != dim_head:
+            raise ValueError(f"dim_head_values ({dim_head_values}) must equal dim_head ({dim_head}) for the "
+                             "sliding-window 2-simplicial kernels")
         attend = partial(sliding_two_simplicial_attn, w1=w1, w2=w2, causal=True)
         super().__init__(*args, number_key_value_sets=2, head_first_dim=False, attend=attend, **kwargs)
         self.w1, self.w2 = w1, w2

@@ -4,25 +4,56 @@ The reference is single-GPU; the operator shards in two ways:
 
 * by (batch, head): every rank runs the operator on its own slice with no
   communication on the data path (``shard_batch_heads``);
-* by sequence blocks for long sequences: rank r owns rows [s_r, e_r) and needs,
-  because the windows are causal, only the LAST ``w1 - 1`` rows of k1/v1 and
-  ``w2 - 1`` rows of k2/v2 of rank r-1 (the "halo").  ``halo_exchange`` fetches
-  them with one point-to-point send/recv per neighbour pair (NCCL on GPUs, gloo
-  on CPU) and prepends them; the kernels take the extended tensors directly
-  (their ``off1/off2`` arguments).  In the backward pass the gradient rows that
-  belong to the halo travel the other way and are added to the owner's tail
-  rows, which autograd does through ``HaloExchange.backward``.
+* by sequence blocks for long sequences (``sequence_parallel_attn``): rank r
+  owns rows [s_r, e_r) and needs, because the windows are causal, only the LAST
+  ``w1 - 1`` rows of k1/v1 and ``w2 - 1`` rows of k2/v2 of rank r-1 (the
+  "halo").  All four halos travel in ONE batched point-to-point exchange per
+  direction (NCCL on GPUs, gloo on CPU), and the exchange overlaps the work that
+  does not need it:
+
+  forward   post the exchange; run the interior query rows (local row >= r0,
+            r0 = the halo length rounded up to the 128-row tile - they see local
+            keys only); wait; run the first r0 rows against [halo | first r0
+            local key rows].
+  backward  run the backward of the first r0 rows (it yields the gradient rows
+            that belong to the halo); post the exchange of those rows; run the
+            interior backward; wait; add the rows received from rank r+1 to the
+            tail of the local key/value gradients.
+
+  The kernels take the extended key tensors directly (their ``off1/off2``
+  arguments) and write their results into views of the result tensors, so no
+  full-size tensor is copied or concatenated.
 
 No collective (all-reduce, all-gather) is needed for the operator itself.
+
+Failure handling: the exchange has a time limit.  With a host-driven backend
+(gloo) every request is waited for with that limit; with NCCL the requests are
+ordered on the stream (no host block) unless ``blocking=True``.  A limit that
+runs out, or a peer that has gone away, raises ``HaloExchangeError`` - the
+caller learns of it on the host and no kernel waits for a peer.
 """
 from __future__ import annotations
+
+import datetime
 
 import torch
 import torch.distributed as dist
 from torch import Tensor
 from torch.autograd import Function
 
-from .attention import sliding_two_simplicial_attn
+from .attention import sa2_backward, sa2_forward
+
+TILE = 128      # query rows per CTA of the kernels: the interior launch starts on a tile boundary
+
+
+class HaloExchangeError(RuntimeError):
+    """The halo exchange with a neighbouring rank failed or ran out of time.  ``status`` is
+    ``"timeout"`` or ``"peer"``; ``rank`` the local rank; ``direction`` ``"forward"`` (keys/values
+    from rank-1) or ``"backward"`` (gradient rows from rank+1)."""
+
+    def __init__(self, status: str, rank: int, direction: str, detail: str = ""):
+        self.status, self.rank, self.direction = status, rank, direction
+        super().__init__(f"halo exchange ({direction}) failed on rank {rank}: {status}" + (f" ({detail})" if detail else ""))
 
 
 def shard_batch_heads(t: Tensor, rank: int, world: int, dim: int = 0) -> Tensor:
@@ -33,103 +64,158 @@ def shard_batch_heads(t: Tensor, rank: int, world: int, dim: int = 0) -> Tensor:
     return t.narrow(dim, rank * step, step)
 
 
-def _via_host(send, recv, group, fn) -> bool:
-    """gloo moves host memory only: stage device tensors through the host (tests on one GPU)."""
-    tensors = (send or []) + (recv or [])
-    if dist.get_backend(group) != "gloo" or not any(t.is_cuda for t in tensors):
-        return False
-    send_h = [t.cpu() for t in send] if send is not None else None
-    recv_h = [torch.empty(t.shape, dtype=t.dtype) for t in recv] if recv is not None else None
-    fn(send_h, recv_h, group)
-    if recv is not None:
-        for d, h in zip(recv, recv_h):
-            d.copy_(h)
-    return True
+class _Exchange:
+    """One batched exchange in flight: ``send`` tensors go to rank ``dst``, ``recv`` tensors are filled
+    from rank ``src`` (either side may be absent).  gloo moves host memory only, so device tensors are
+    staged through the host there (tests that run several ranks on one GPU)."""
+
+    def __init__(self, send, dst, recv, src, group, direction):
+        self.group, self.direction = group, direction
+        self.rank = dist.get_rank(group)
+        self.recv, self.staged = recv, None
+        backend = dist.get_backend(group)
+        self.host_driven = backend != "nccl"
+        if backend == "gloo" and any(t.is_cuda for t in (send or []) + (recv or [])):
+            send = [t.cpu() for t in send] if send else send
+            self.staged = [torch.empty(t.shape, dtype=t.dtype) for t in recv] if recv else None
+            recv = self.staged
+        ops = []
+        if recv:
+            peer = dist.get_global_rank(group, src) if group is not None else src
+            ops += [dist.P2POp(dist.irecv, t, peer, group) for t in recv]
+        if send:
+            peer = dist.get_global_rank(group, dst) if group is not None else dst
+            ops += [dist.P2POp(dist.isend, t, peer, group) for t in send]
+        self.keep = (send, recv)
+        try:
+            self.reqs = dist.batch_isend_irecv(ops) if ops else []
+        except RuntimeError as e:
+            raise HaloExchangeError("peer", self.rank, direction, str(e)) from e
+
+    def wait(self, timeout: float | None, blocking: bool = False):
+        """Order the received data before whatever the caller launches next.  Host-driven backends (and
+        ``blocking``) wait on the host for at most ``timeout`` seconds."""
+        limit = datetime.timedelta(seconds=timeout) if timeout is not None else None
+        for req in self.reqs:
+            try:
+                if (self.host_driven or blocking) and limit is not None:
+                    ok = req.wait(limit)
+                else:
+                    ok = req.wait()
+            except RuntimeError as e:
+                msg = str(e).lower()
+                status = "timeout" if ("timed out" in msg or "timeout" in msg) else "peer"
+                raise HaloExchangeError(status, self.rank, self.direction, str(e).splitlines()[0]) from e
+            if ok is False:
+                raise HaloExchangeError("timeout", self.rank, self.direction)
+        if self.staged is not None:
+            for d_, h_ in zip(self.recv, self.staged):
+                d_.copy_(h_)
+        self.reqs = []
 
 
-def _exchange(send_right: list[Tensor] | None, recv_left: list[Tensor] | None, group) -> None:
-    """One step of the chain: post every send to rank+1 and every recv from rank-1, then wait."""
-    if _via_host(send_right, recv_left, group, _exchange):
-        return
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    ops = []
-    if recv_left is not None and rank > 0:
-        src = dist.get_global_rank(group, rank - 1) if group is not None else rank - 1
-        ops += [dist.P2POp(dist.irecv, t, src, group) for t in recv_left]
-    if send_right is not None and rank < world - 1:
-        dst = dist.get_global_rank(group, rank + 1) if group is not None else rank + 1
-        ops += [dist.P2POp(dist.isend, t, dst, group) for t in send_right]
-    if ops:
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
+def _cuda_forward(q, k1, k2, v1, v2, w1, w2, out=None, **kw):
+    return sa2_forward(q, k1, k2, v1, v2, w1, w2, out=out, **kw)
 
 
-def _exchange_back(send_left: list[Tensor] | None, recv_right: list[Tensor] | None, group) -> None:
-    """The mirror step: sends go to rank-1, receives come from rank+1."""
-    if _via_host(send_left, recv_right, group, _exchange_back):
-        return
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    ops = []
-    if recv_right is not None and rank < world - 1:
-        src = dist.get_global_rank(group, rank + 1) if group is not None else rank + 1
-        ops += [dist.P2POp(dist.irecv, t, src, group) for t in recv_right]
-    if send_left is not None and rank > 0:
-        dst = dist.get_global_rank(group, rank - 1) if group is not None else rank - 1
-        ops += [dist.P2POp(dist.isend, t, dst, group) for t in send_left]
-    if ops:
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
+def _cuda_backward(q, k1, k2, v1, v2, out, lse, dout, w1, w2, grads=None, **kw):
+    return sa2_backward(q, k1, k2, v1, v2, out, lse, dout, w1, w2, grads=grads, **kw)
 
 
-class HaloExchange(Function):
-    """``apply(t, rows, group)``: returns ``cat(last `rows` rows of rank-1's t, t)`` along
-    the sequence dim (1).  Rank 0 has no left neighbour and returns ``t`` itself.
-    Backward: the gradient of the halo rows is sent to rank-1, which adds it to the
-    gradient of its last ``rows`` rows."""
+class SequenceParallelAttention(Function):
+    """Autograd function behind ``sequence_parallel_attn``: the schedule described in the module
+    docstring.  ``engine = (forward, backward)`` are the block-local operators
+    ``forward(q, k1, k2, v1, v2, w1, w2, out=view) -> (out, lse)`` and
+    ``backward(q, k1, k2, v1, v2, out, lse, dout, w1, w2, grads=views) -> 5 gradients``; keys / values may
+    carry leading halo rows.  The default engine is the CUDA library."""
 
     @staticmethod
-    def forward(ctx, t: Tensor, rows: int, group=None):
+    def forward(ctx, q, k1, k2, v1, v2, w1, w2, group, engine, timeout, blocking, kw):
+        fwd, _ = engine
         rank, world = dist.get_rank(group), dist.get_world_size(group)
-        ctx.rows, ctx.group, ctx.rank, ctx.world = rows, group, rank, world
-        if rows <= 0 or world == 1:
-            ctx.rows = 0
-            return t.view_as(t)
-        assert t.shape[1] >= rows, "a sequence block must be at least as long as the halo (w - 1 rows)"
-        tail = t[:, -rows:].contiguous()
-        halo = torch.empty_like(tail)
-        _exchange([tail], [halo], group)
-        return torch.cat([halo, t], dim=1) if rank > 0 else t.view_as(t)
+        n = q.shape[1]
+        h1, h2 = min(w1 - 1, n), min(w2 - 1, n)
+        assert world == 1 or n >= max(w1, w2) - 1, "a sequence block must be at least as long as the halo (w - 1 rows)"
+        if world == 1:
+            h1 = h2 = 0
+        # rows [r0, n) see local keys only
+        r0 = min(n, -(-max(h1, h2) // TILE) * TILE) if rank > 0 else 0
+        ex = None
+        halos = None
+        if world > 1:
+            send = [k1[:, n - h1:].contiguous(), v1[:, n - h1:].contiguous(),
+                    k2[:, n - h2:].contiguous(), v2[:, n - h2:].contiguous()] if rank < world - 1 else None
+            halos = [torch.empty_like(k1[:, :h1]), torch.empty_like(v1[:, :h1]),
+                     torch.empty_like(k2[:, :h2]), torch.empty_like(v2[:, :h2])] if rank > 0 else None
+            ex = _Exchange(send, rank + 1, halos, rank - 1, group, "forward")
+        out = torch.empty_like(q)
+        lse_i = lse_b = None
+        if r0 < n:      # interior rows (all rows on rank 0): no halo needed
+            _, lse_i = fwd(q[:, r0:], k1[:, r0 - h1 if rank > 0 else 0:], k2[:, r0 - h2 if rank > 0 else 0:],
+                           v1[:, r0 - h1 if rank > 0 else 0:], v2[:, r0 - h2 if rank > 0 else 0:], w1, w2, out=out[:, r0:], **kw)
+        if ex is not None:
+            ex.wait(timeout, blocking)
+        if rank > 0:    # the first r0 rows against [halo | first r0 local rows]
+            ext = [torch.cat((h_, t[:, :r0]), dim=1) for h_, t in zip(halos, (k1, v1, k2, v2))]
+            _, lse_b = fwd(q[:, :r0], ext[0], ext[2], ext[1], ext[3], w1, w2, out=out[:, :r0], **kw)
+        ctx.save_for_backward(q, k1, k2, v1, v2, out, lse_i, lse_b, *(halos or []))
+        ctx.cfg = (w1, w2, group, engine, timeout, blocking, kw, rank, world, n, h1, h2, r0)
+        return out
 
     @staticmethod
-    def backward(ctx, grad: Tensor):
-        rows, group, rank, world = ctx.rows, ctx.group, ctx.rank, ctx.world
-        if rows == 0:
-            return grad, None, None
+    def backward(ctx, dout):
+        w1, w2, group, engine, timeout, blocking, kw, rank, world, n, h1, h2, r0 = ctx.cfg
+        _, bwd = engine
+        q, k1, k2, v1, v2, out, lse_i, lse_b, *halos = ctx.saved_tensors
+        dout = dout.contiguous() if dout.stride(-1) != 1 else dout
+        grads = [torch.empty_like(t) for t in (q, k1, k2, v1, v2)]
+        dq, dk1, dk2, dv1, dv2 = grads
+        ex = None
+        bnd = None
         if rank > 0:
-            g_halo, g_own = grad[:, :rows].contiguous(), grad[:, rows:]
-        else:
-            g_halo, g_own = None, grad
-        g_from_right = torch.empty_like(g_own[:, -rows:]).contiguous() if rank < world - 1 else None
-        _exchange_back([g_halo] if g_halo is not None else None,
-                       [g_from_right] if g_from_right is not None else None, group)
-        if g_from_right is not None:
-            g_own = g_own.clone()
-            g_own[:, -rows:] += g_from_right
-        return g_own, None, None
+            # the first r0 rows first: their backward yields the gradient rows of the halo
+            ext = [torch.cat((h_, t[:, :r0]), dim=1) for h_, t in zip(halos, (k1, v1, k2, v2))]
+            bnd = bwd(q[:, :r0], ext[0], ext[2], ext[1], ext[3], out[:, :r0], lse_b, dout[:, :r0], w1, w2, **kw)
+        if world > 1:
+            send = [bnd[1][:, :h1].contiguous(), bnd[3][:, :h1].contiguous(),
+                    bnd[2][:, :h2].contiguous(), bnd[4][:, :h2].contiguous()] if rank > 0 else None
+            recv = [torch.empty_like(k1[:, :h1]), torch.empty_like(v1[:, :h1]),
+                    torch.empty_like(k2[:, :h2]), torch.empty_like(v2[:, :h2])] if rank < world - 1 else None
+            ex = _Exchange(send, rank - 1, recv, rank + 1, group, "backward")
+        if r0 < n:
+            # interior rows: written straight into the rows [r0 - halo, n) of the local gradients
+            a1, a2 = (r0 - h1, r0 - h2) if rank > 0 else (0, 0)
+            bwd(q[:, r0:], k1[:, a1:], k2[:, a2:], v1[:, a1:], v2[:, a2:], out[:, r0:], lse_i, dout[:, r0:], w1, w2,
+                grads=(dq[:, r0:], dk1[:, a1:], dk2[:, a2:], dv1[:, a1:], dv2[:, a2:]), **kw)
+        if rank > 0:
+            # local rows [0, r0) of the first launch: rows below the interior's range are its alone, the
+            # overlap [r0 - halo, r0) has a contribution from both launches
+            dq[:, :r0] = bnd[0]
+            for g_, b_, h_ in ((dk1, bnd[1], h1), (dk2, bnd[2], h2), (dv1, bnd[3], h1), (dv2, bnd[4], h2)):
+                loc = b_[:, h_:]                     # rows [0, r0) of the local tensor
+                lo = r0 - h_ if r0 < n else r0       # first local row the interior launch has written
+                g_[:, :lo] = loc[:, :lo]
+                if lo < r0:
+                    g_[:, lo:r0] += loc[:, lo:r0]
+        if ex is not None:
+            ex.wait(timeout, blocking)
+            if rank < world - 1:
+                for g_, r_, h_ in zip((dk1, dv1, dk2, dv2), ex.recv, (h1, h1, h2, h2)):
+                    g_[:, n - h_:] += r_
+        return (dq, dk1, dk2, dv1, dv2) + (None,) * 7
 
 
-def halo_exchange(t: Tensor, rows: int, group=None) -> Tensor:
-    return HaloExchange.apply(t, rows, group)
-
-
-def sequence_parallel_attn(q: Tensor, keys, values, w1=512, w2=32, group=None, attend=None, **kw):
+def sequence_parallel_attn(q: Tensor, keys, values, w1=512, w2=32, group=None, engine=None, timeout: float | None = 60.0,
+                           blocking: bool = False, **kw):
     """Sliding-window 2-simplicial attention over a sequence split into contiguous
     blocks, one per rank of ``group`` in rank order.  Inputs and the result are the
-    local block ``(b, n_local, h, d)``.  ``attend`` defaults to the CUDA operator; the
-    CPU tests pass an oracle with the same signature."""
-    attend = sliding_two_simplicial_attn if attend is None else attend
+    local block ``(b, n_local, h, d)``.  ``engine`` defaults to the CUDA library; the
+    CPU tests pass an oracle pair.  ``timeout`` (seconds) bounds every wait of a
+    host-driven exchange; see the module docstring."""
+    engine = (_cuda_forward, _cuda_backward) if engine is None else engine
     k1, k2 = keys
     v1, v2 = values
-    k1e, v1e = halo_exchange(k1, w1 - 1, group), halo_exchange(v1, w1 - 1, group)
-    k2e, v2e = halo_exchange(k2, w2 - 1, group), halo_exchange(v2, w2 - 1, group)
-    return attend(q, (k1e, k2e), (v1e, v2e), w1=w1, w2=w2, causal=True, **kw)
+    if q.is_cuda and torch.is_autocast_enabled():
+        dt = torch.get_autocast_dtype("cuda")
+        q, k1, k2, v1, v2 = (t.to(dt) for t in (q, k1, k2, v1, v2))
+    return SequenceParallelAttention.apply(q, k1, k2, v1, v2, int(w1), int(w2), group, engine, timeout, blocking, kw)
