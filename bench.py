@@ -54,6 +54,9 @@ WORKLOADS = {
     "C2": dict(b=2, hq=8, hk=8, n=1024, d=64, w1=512, w2=32),
     "C3": dict(b=4, hq=8, hk=8, n=4096, d=64, w1=512, w2=32),
     "C5": dict(b=8, hq=16, hk=16, n=16384, d=128, w1=512, w2=32),
+    # two (batch, head) pairs of C5 and one batch element of C3: small cases for profiler captures
+    "C5s": dict(b=1, hq=2, hk=2, n=16384, d=128, w1=512, w2=32),
+    "C3s": dict(b=1, hq=8, hk=8, n=4096, d=64, w1=512, w2=32),
 }
 # CPU sample: two batch elements, eight heads, up to 4096 rows of the same head dim and windows (~10 s on 16 cores)
 CPU_SAMPLE = dict(b=2, hq=8, hk=8, n=4096)
@@ -509,6 +512,8 @@ def main():
 
     dtype = torch.bfloat16
     big = args.workload == "C5"
+    if args.workload in ("C5s", "C3s"):
+        args.no_extra = args.no_e2e = args.no_cpu_baseline = True
     host, devt = make_inputs(cfg, seed=1234 + rank, dtype=dtype, device=dev, pin=not (args.no_e2e or big))
     w1, w2 = cfg["w1"], cfg["w2"]
     fl = work_flops(cfg)

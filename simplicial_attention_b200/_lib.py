@@ -75,7 +75,8 @@ _lib = None
 
 
 def lib_path() -> str:
-    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "libsa2.so")
+    """``SA2_LIBRARY`` names another build of the library (for example a diagnostic build with wait accounting)."""
+    return os.environ.get("SA2_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libsa2.so")
 
 
 def lib() -> C.CDLL:
@@ -88,7 +89,7 @@ def lib() -> C.CDLL:
             return _lib
         path = lib_path()
         from . import build
-        if os.environ.get("SA2_REBUILD") or build.is_stale():
+        if not os.environ.get("SA2_LIBRARY") and (os.environ.get("SA2_REBUILD") or build.is_stale()):
             build.build(force=bool(os.environ.get("SA2_REBUILD")))
         handle = C.CDLL(path)
         handle.sa2_fwd.argtypes = [C.POINTER(FwdArgs)]

@@ -92,6 +92,15 @@ extern "C" {
 
 int sa2_version(void) { return 100; }
 
+#ifdef SA2_PROF
+// diagnostic builds only (-DSA2_PROF=<CTA index>): read and clear the wait-accounting table
+int sa2_prof_read(unsigned long long *host, int n) {
+    if (cudaMemcpyFromSymbol(host, sa2::sm100::g_prof, sizeof(unsigned long long) * n) != cudaSuccess) return -1;
+    static unsigned long long zeros[512] = {0};
+    return cudaMemcpyToSymbol(sa2::sm100::g_prof, zeros, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
+}
+#endif
+
 int sa2_device_status(int reset) {
     int *word = sa2::tc::status_word();
     if (!word) return -1;

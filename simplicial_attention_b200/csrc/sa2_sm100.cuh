@@ -40,13 +40,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Optional wait accounting (compile with -DSA2_PROF): lane 0 of every warp of one CTA adds the cycles
+// it spends in a wait to g_prof[8 * warp + slot]; sa2_prof_read() copies the table to the host.
+#ifdef SA2_PROF
+__device__ unsigned long long g_prof[512];
+__device__ __forceinline__ void prof_add(int slot, long long cycles) {
+    if (slot >= 0 && blockIdx.x == SA2_PROF && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0)
+        g_prof[(threadIdx.x >> 5) * 8 + slot] += (unsigned long long)cycles;
+}
+#define SA2_PROF_ADD(slot, cycles) sa2::sm100::prof_add(slot, cycles)
+// segment timing: SA2_PROF_MARK(t) starts a segment, SA2_PROF_LAP(slot, t) books the time since and restarts
+#define SA2_PROF_MARK(t) long long t = clock64()
+#define SA2_PROF_LAP(slot, t) do { const long long _n = clock64(); sa2::sm100::prof_add(slot, _n - t); t = _n; } while (0)
+#else
+#define SA2_PROF_ADD(slot, cycles) do { } while (0)
+#define SA2_PROF_MARK(t) do { } while (0)
+#define SA2_PROF_LAP(slot, t) do { } while (0)
+#endif
+
 // Bounded wait.  `abort_flag` is a CTA-wide shared word: once any thread gives
-// up, every later wait in the CTA returns false at once.
+// up, every later wait in the CTA returns false at once.  `prof` names the accounting slot (see above).
 // `sleep_ns` > 0 makes the poller yield its issue slots between tries (used by
 // whole warps that wait; the single MMA-issuing lanes poll without sleeping).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned sleep_ns = 0) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned sleep_ns = 0,
+                                          int prof = -1) {
+#ifdef SA2_PROF
+    const long long t0 = clock64();       // a try_wait may suspend the thread: the first try counts as waiting too
+    if (mbar_try_wait(bar, parity)) { SA2_PROF_ADD(prof, clock64() - t0); return true; }
+#else
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+#endif
     int spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if (sleep_ns) __nanosleep(sleep_ns);
@@ -58,6 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
             }
         }
     }
+    SA2_PROF_ADD(prof, clock64() - t0);
     return true;
 }
 

@@ -20,9 +20,12 @@
 //     products into a TMEM half wait until the second products that read it
 //     are done;
 //   * a step covers a block of 64 query rows (not 128), so that an (A_e, B_e)
-//     stage is 32 KB and two stages, the resident K1/V1 tile (64 KB) and the
-//     staged second-key window fit together; consecutive steps alternate
-//     between the two TMEM halves and their compute groups;
+//     stage is 32 KB and three stages, the resident K1/V1 tile (64 KB) and the
+//     staged second-key window fit together (a stage is held from its build
+//     through both products and the exponent pass between them, ~4800 cycles,
+//     so two stages paced a step at ~2900 cycles); consecutive steps alternate
+//     between the two TMEM halves and their compute groups; the constant tile
+//     of ones and three slots of per-query statistics share one 16 KB tile;
 //   * the k2 / v2 rows a query block pairs with over all sweeps (64 + 32 rows of
 //     each) are staged once per block by TMA; four builder threads per query row
 //     hold 32 channels of q_i and dO_i in registers for the whole block and form
@@ -48,7 +51,7 @@ constexpr int THREADS = 640;
 constexpr int REGS_LAUNCH = 96, REGS_ISSUE = 40, REGS_COMPUTE = 128, REGS_BUILD = 88;
 static_assert(REGS_ISSUE + 2 * REGS_COMPUTE + 2 * REGS_BUILD <= 5 * REGS_LAUNCH, "register pool must balance");
 constexpr int QB = 64;                            // query rows per step
-constexpr int STAGES = 2;
+constexpr int STAGES = 3;
 constexpr uint32_t BLK_BYTES = TJ * 128;          // K1 / V1: one [128 rows][64 channels] swizzled block
 constexpr uint32_t T_BYTES = 2 * BLK_BYTES;       // the 128-row tile of 128 channels
 constexpr uint32_t QBLK_BYTES = QB * 128;         // A_e / B_e: one [64 rows][64 channels] block
@@ -60,16 +63,23 @@ constexpr uint32_t WIN_BYTES = 2 * WBLK_BYTES;    // k2 (or v2) window
 
 enum Bar {
     B_KV_FULL = 0,
-    B_AB_FULL = 1,       // [STAGES]
-    B_AB_EMPTY = 3,      // [STAGES]
-    B_S_FULL = 5,        // [2] per TMEM half
-    B_P_FULL = 7,        // [2]
-    B_G_DONE = 9,        // [2] second products of the step have completed
-    B_DONE = 11,
-    B_WIN_FREE = 12,     // the builders have finished reading the previous block's window
-    B_WIN_FULL = 13,
-    B_COUNT = 14
+    B_AB_FULL = 1,                      // [STAGES]
+    B_AB_EMPTY = B_AB_FULL + STAGES,    // [STAGES]
+    B_S_FULL = B_AB_EMPTY + STAGES,     // [2] per TMEM half
+    B_P_FULL = B_S_FULL + 2,            // [2]
+    B_G_DONE = B_P_FULL + 2,            // [2] second products of the step have completed
+    B_DONE = B_G_DONE + 2,
+    B_WIN_FREE = B_DONE + 1,            // the builders have finished reading the previous block's window
+    B_WIN_FULL = B_WIN_FREE + 1,
+    B_COUNT = B_WIN_FULL + 1
 };
+
+// The constant tile: a [128 rows][128 bytes] swizzled tile whose 16-byte chunks 0-1 hold the key-side ones
+// (rows = key rows) and whose other chunks hold three slots of query statistics (rows = query rows of a
+// block): slot k < 2 has its -lse2/c slab in chunks 2-3 and its -D slab in chunks 4-5 of rows [64 k, +64);
+// slot 2 has -lse2/c in chunks 6-7 of rows [0, 64) and -D in chunks 6-7 of rows [64, 128).
+__device__ __forceinline__ int stat_row(int slot, int which, int r) { return slot < 2 ? 64 * slot + r : 64 * which + r; }
+__device__ __forceinline__ int stat_chunk(int slot, int which) { return slot < 2 ? 2 + 2 * which : 6; }
 
 struct Params {
     KernelParams kp;
@@ -79,7 +89,7 @@ struct Params {
 };
 
 inline size_t smem_bytes() {
-    return 1024 + 2 * T_BYTES + STAGES * STAGE_BYTES + 2 * TILE_BYTES + 2 * WIN_BYTES + B_COUNT * 8 + 64;
+    return 1024 + 2 * T_BYTES + STAGES * STAGE_BYTES + TILE_BYTES + 2 * WIN_BYTES + B_COUNT * 8 + 64;
 }
 
 struct Geom {
@@ -107,7 +117,7 @@ __device__ __forceinline__ Geom geom(const KernelParams &kp) {
 // ---------------------------------------------------------------- builders (warps 12-19)
 // Thread (r, part): query row r of the block, channels [32 part, +32).
 __device__ __forceinline__ int builder(const Params &P, const Geom &g, const CUtensorMap *mapK2, const CUtensorMap *mapV2,
-                                       uint8_t *sAB, uint8_t *sStat, uint8_t *sOnes, uint8_t *sWin,
+                                       uint8_t *sAB, uint8_t *sConst, uint8_t *sWin,
                                        uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int bt = threadIdx.x - 384;      // 0..255 among the builders
@@ -119,11 +129,9 @@ __device__ __forceinline__ int builder(const Params &P, const Geom &g, const CUt
     const __nv_bfloat16 *dout = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p);
     const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p);
     if (bt < 128) {
-        // the constant key-side tile: three ones per row (one per term of the split statistics)
-        const uint4 one = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc)
-            *reinterpret_cast<uint4 *>(sOnes + sw128_offset(bt, cc)) = cc == 0 ? one : make_uint4(0u, 0u, 0u, 0u);
+        // the key-side ones: three per row (one per term of the split statistics), then zeros up to K = 16
+        *reinterpret_cast<uint4 *>(sConst + sw128_offset(bt, 0)) = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
+        *reinterpret_cast<uint4 *>(sConst + sw128_offset(bt, 1)) = make_uint4(0u, 0u, 0u, 0u);
     }
     const float inv_c = 1.f / P.c;
     const bool win = kp.w2 <= 32;
@@ -166,18 +174,18 @@ __device__ __forceinline__ int builder(const Params &P, const Geom &g, const CUt
                 if (part == 0) stat = -kp.lse[o] * 1.4426950408889634f * inv_c;
                 else if (part == 1) stat = -kp.delta[o];
             }
-            if (win && !mbar_wait(&bars[B_WIN_FULL], blk & 1, abort_flag, 64)) return ERR_BK1_BUILDER;
+            if (win && !mbar_wait(&bars[B_WIN_FULL], blk & 1, abort_flag, 64, 1)) return ERR_BK1_BUILDER;
             for (int e = 0; e < ne; ++e, ++s) {
                 const int stage = s % STAGES;
-                // the stage is free once the second products of two steps ago have completed
-                if (s >= STAGES && !warp_wait(&bars[B_AB_EMPTY + stage], (s / STAGES - 1) & 1, abort_flag)) return ERR_BK1_BUILDER;
+                // the stage is free once the second products of three steps ago have completed
+                if (s >= STAGES && !warp_wait(&bars[B_AB_EMPTY + stage], (s / STAGES - 1) & 1, abort_flag, 2)) return ERR_BK1_BUILDER;
                 if (e == 0 && part < 2) {
-                    // Statistics of this query block: K = 16 slabs of -lse2/c (chunks 0-1) and -D (chunks 2-3) in
-                    // rows [64 (blk & 1), +64) of the statistics tile.  Step s - 2 has completed and every block
-                    // has at least one step, so the slabs of two blocks ago are no longer read.
-                    const int row = (blk & 1) * QB + r;
-                    *reinterpret_cast<uint4 *>(sStat + sw128_offset(row, part * 2)) = split3_bf16(stat);
-                    *reinterpret_cast<uint4 *>(sStat + sw128_offset(row, part * 2 + 1)) = make_uint4(0u, 0u, 0u, 0u);
+                    // Statistics of this query block (K = 16 slabs of -lse2/c and of -D) in slot blk % 3.  Step
+                    // s - 3 has completed and every block has at least one step, so the slabs of three blocks ago
+                    // are no longer read.
+                    const int row = stat_row(blk % 3, part, r), ch = stat_chunk(blk % 3, part);
+                    *reinterpret_cast<uint4 *>(sConst + sw128_offset(row, ch)) = split3_bf16(stat);
+                    *reinterpret_cast<uint4 *>(sConst + sw128_offset(row, ch + 1)) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 uint8_t *dA = sAB + (size_t)stage * STAGE_BYTES + (size_t)cb * QBLK_BYTES;
                 uint8_t *dB = dA + AB_BYTES;
@@ -212,25 +220,25 @@ __device__ __forceinline__ int builder(const Params &P, const Geom &g, const CUt
 }
 
 // ---------------------------------------------------------------- issuers of S^T (warp 1) and dP^T (warp 2), one lane each
-// Step s uses stage s % 2 and TMEM half s % 2.
+// Step s uses stage s % 3 and TMEM half s % 2.
 __device__ __forceinline__ int mma_first(const KernelParams &kp, const Geom &g, int which, uint32_t tmem, uint8_t *sKV,
-                                         uint8_t *sAB, uint8_t *sStat, uint8_t *sOnes, uint64_t *bars, volatile int *abort_flag) {
+                                         uint8_t *sAB, uint8_t *sConst, uint64_t *bars, volatile int *abort_flag) {
     constexpr uint32_t IDESC_F = idesc_bf16(128, 64, false, false);
     const uint64_t dT = smem_desc_sw128(smem_u32(sKV));
     const uint64_t dAB = smem_desc_sw128(smem_u32(sAB + which * AB_BYTES));
-    const uint64_t dSt = smem_desc_sw128(smem_u32(sStat)), dOnes = smem_desc_sw128(smem_u32(sOnes));
+    const uint64_t dOnes = smem_desc_sw128(smem_u32(sConst));
     if (!mbar_wait(&bars[B_KV_FULL], 0, abort_flag)) return ERR_BK1_MMA;
     int s = 0, blk = 0;
     for (int hh = 0; hh < kp.g; ++hh) {
         for (int ib = 0; ib < g.n_ib; ++ib, ++blk) {
             const int ne = block_sweeps(kp, g, ib);
-            // this block's slabs: rows [64 (blk & 1), +64) of the statistics tile, chunks 0-1 (lse) or 2-3 (D)
-            const uint64_t st = dSt + (uint64_t)(((blk & 1) * QB * 128) >> 4) + (uint64_t)(which * 2);
+            // this block's slab of the constant tile (rows are multiples of 64: whole 8-row swizzle groups)
+            const uint64_t st = dOnes + (uint64_t)((stat_row(blk % 3, which, 0) * 128) >> 4) + (uint64_t)stat_chunk(blk % 3, which);
             for (int e = 0; e < ne; ++e, ++s) {
-                const int stage = s & 1, half = s & 1;
-                if (!mbar_wait(&bars[B_AB_FULL + stage], (s >> 1) & 1, abort_flag)) return ERR_BK1_MMA;
+                const int stage = s % STAGES, half = s & 1;
+                if (!mbar_wait(&bars[B_AB_FULL + stage], (s / STAGES) & 1, abort_flag, 0, 1)) return ERR_BK1_MMA;
                 // P^T / G^T of the step that used this half last lie over these columns until its second products are done
-                if (s >= 2 && !mbar_wait(&bars[B_G_DONE + half], ((s >> 1) - 1) & 1, abort_flag)) return ERR_BK1_MMA;
+                if (s >= 2 && !mbar_wait(&bars[B_G_DONE + half], ((s >> 1) - 1) & 1, abort_flag, 0, 2)) return ERR_BK1_MMA;
                 tc_fence_after();
                 const uint64_t a = dAB + (uint64_t)((stage * STAGE_BYTES) >> 4);
                 const uint32_t d = tmem + half * 128 + which * 64;
@@ -255,8 +263,8 @@ __device__ __forceinline__ int mma_second(const Params &P, const Geom &g, uint32
     constexpr uint32_t IDESC_G64 = idesc_bf16(128, 64, false, true);
     const uint64_t dAB = smem_desc_sw128(smem_u32(sAB), 1024, QBLK_BYTES);   // channel blocks 8 KB apart
     for (int s = 0; s < g.total; ++s) {
-        const int stage = s & 1, half = s & 1;
-        if (!mbar_wait(&bars[B_P_FULL + half], (s >> 1) & 1, abort_flag)) return ERR_BK1_MMA;
+        const int stage = s % STAGES, half = s & 1;
+        if (!mbar_wait(&bars[B_P_FULL + half], (s >> 1) & 1, abort_flag, 0, 1)) return ERR_BK1_MMA;
         tc_fence_after();
         const uint64_t a = dAB + (uint64_t)((stage * STAGE_BYTES) >> 4), bq = a + (AB_BYTES >> 4);
         const uint32_t tp = tmem + half * 128, tg = tp + 64;
@@ -310,7 +318,7 @@ __device__ __forceinline__ int compute(const Params &P, const Geom &g, int half,
                 for (int e = 0; e < ne; ++e, ++s) {
                     if ((s & 1) != half) continue;
                     const int lo = max(max(0, base), e - kp.off2 - it0);      // valid columns: lo <= col <= hi
-                    if (!warp_wait(&bars[B_S_FULL + half], (s >> 1) & 1, abort_flag)) return ERR_BK1_COMPUTE;
+                    if (!warp_wait(&bars[B_S_FULL + half], (s >> 1) & 1, abort_flag, 1)) return ERR_BK1_COMPUTE;
                     tc_fence_after();
                     const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
 #pragma unroll
@@ -390,9 +398,8 @@ bwd_k1_128_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
     uint8_t *sK = smem;
     uint8_t *sV = sK + T_BYTES;
     uint8_t *sAB = sV + T_BYTES;                          // STAGES x (A_e, B_e)
-    uint8_t *sStat = sAB + STAGES * STAGE_BYTES;          // two slots of 64 rows x (-lse2/c slab, -D slab)
-    uint8_t *sOnes = sStat + TILE_BYTES;                  // constant: three ones per row
-    uint8_t *sWin = sOnes + TILE_BYTES;                   // staged k2 window, then v2 window
+    uint8_t *sConst = sAB + STAGES * STAGE_BYTES;         // ones and three slots of query statistics
+    uint8_t *sWin = sConst + TILE_BYTES;                  // staged k2 window, then v2 window
     uint64_t *bars = reinterpret_cast<uint64_t *>(sWin + 2 * WIN_BYTES);
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + B_COUNT);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
@@ -420,6 +427,9 @@ bwd_k1_128_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
     const Geom g = geom(P.kp);
 
     int err = 0;
+#ifdef SA2_PROF
+    const long long prof_t0 = clock64();
+#endif
     if (warp < 4) {
         reg_dealloc<REGS_ISSUE>();
         if (warp == 0) {
@@ -442,7 +452,7 @@ bwd_k1_128_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
             __syncwarp();
         } else if (warp == 1 || warp == 2) {
             if (lane == 0 && g.total > 0)
-                err = mma_first(P.kp, g, warp - 1, tmem, warp == 1 ? sK : sV, sAB, sStat, sOnes, bars, abort_flag);
+                err = mma_first(P.kp, g, warp - 1, tmem, warp == 1 ? sK : sV, sAB, sConst, bars, abort_flag);
             __syncwarp();
         }
     } else if (warp < 12) {
@@ -450,9 +460,10 @@ bwd_k1_128_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constan
         err = compute(P, g, (warp - 4) >> 2, tmem, bars, abort_flag);
     } else {
         reg_dealloc<REGS_BUILD>();
-        err = builder(P, g, &mapK2, &mapV2, sAB, sStat, sOnes, sWin, bars, abort_flag);
+        err = builder(P, g, &mapK2, &mapV2, sAB, sConst, sWin, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
+    SA2_PROF_ADD(0, clock64() - prof_t0);
 
     tc_fence_before();
     __syncthreads();

@@ -31,8 +31,9 @@
 // sweep, so the read-modify-write needs no atomics.
 //
 // Warps (512 threads, four aligned warpgroups): 0 TMA producer, then issuer of U / W; 1 TMEM owner and
-// issuer of S; 2 issuer of dP; 3 idle; 4-7 compute (P, G); 8-11 fold (U, W into dQ / dK2 / dV2, concurrently with
-// the next sweep's compute); 12-15 builders.  Every thread starts with 128 registers; the issuer
+// issuer of S; 2 issuer of dP; 3 idle (head dim 128: TMA producer of the ring); 4-7 compute (P, G); 8-11 fold
+// (U, W into dQ / dK2 / dV2, concurrently with the next sweep's compute; head dim 128: also forms B_e);
+// 12-15 builders.  Every thread starts with 128 registers; the issuer
 // warpgroup releases all but 24 (setmaxnreg) and the fold and builder groups take them over.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
 // 128h+128); sweep parity p -> U [256+128p, +64), W [320+128p, +64).
 #pragma once
@@ -179,7 +180,7 @@ __device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, ui
                     vv[cc] = *reinterpret_cast<const uint4 *>(vp2 + cc * 8);
                 }
             }
-            if (v >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (v - 1) & 1, abort_flag)) return ERR_BQ_BUILDER;
+            if (v >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (v - 1) & 1, abort_flag, 1)) return ERR_BQ_BUILDER;
 #pragma unroll
             for (int cc = 0; cc < 8; ++cc) {
                 uint4 a = make_uint4(0, 0, 0, 0), bb = make_uint4(0, 0, 0, 0);
@@ -196,39 +197,26 @@ __device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, ui
             mbar_arrive(&bars[BQ_AB_FULL]);
         }
     } else {
+        // head dim 128: this group forms A_e only (the fold group forms B_e, see bq_build_b); the whole row is
+        // fetched before the wait, so that the stage is rebuilt as soon as the tensor cores release it
         for (int v = 0; v < nv; ++v) {
             const int e = v;
             const int kk = i + kp.off2 - e;
             const bool ok = iv && kk >= 0;
             const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
-            const __nv_bfloat16 *vp2 = v2 + elem_off(kp.v2, b, ok ? kk : 0, hk);
+            uint4 qv[16], kv[16];
 #pragma unroll
-            for (int cb = 0; cb < 2; ++cb) {
-                uint4 qv[8], dv[8], kv[8], vv[8];
+            for (int cc = 0; cc < 16; ++cc) {
+                qv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(qp + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                kv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kp2 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (v >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (v - 1) & 1, abort_flag, 1)) return ERR_BQ_BUILDER;
 #pragma unroll
-                for (int cc = 0; cc < 8; ++cc) {
-                    const int c8 = cb * 64 + cc * 8;
-                    if (ok) {
-                        qv[cc] = __ldg(reinterpret_cast<const uint4 *>(qp + c8));
-                        dv[cc] = __ldg(reinterpret_cast<const uint4 *>(dp + c8));
-                        kv[cc] = __ldg(reinterpret_cast<const uint4 *>(kp2 + c8));
-                        vv[cc] = __ldg(reinterpret_cast<const uint4 *>(vp2 + c8));
-                    } else {
-                        qv[cc] = dv[cc] = kv[cc] = vv[cc] = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                }
-                // the loads of the first block are in flight while the previous sweep still reads the stage
-                if (cb == 0 && v >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (v - 1) & 1, abort_flag)) return ERR_BQ_BUILDER;
-#pragma unroll
-                for (int cc = 0; cc < 8; ++cc) {
-                    uint4 a, bb;
-                    a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
-                    a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
-                    bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
-                    bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
-                    *reinterpret_cast<uint4 *>(sA + cb * BqCfg<D>::BLK + sw128_offset(r, cc)) = a;
-                    *reinterpret_cast<uint4 *>(sB + cb * BqCfg<D>::BLK + sw128_offset(r, cc)) = bb;
-                }
+            for (int cc = 0; cc < 16; ++cc) {
+                uint4 a;
+                a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
+                a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
+                *reinterpret_cast<uint4 *>(sA + (cc >> 3) * BqCfg<D>::BLK + sw128_offset(r, cc & 7)) = a;
             }
             fence_proxy_async_smem();
             mbar_arrive(&bars[BQ_AB_FULL]);
@@ -253,15 +241,15 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t
     }
     int u = 0;
     for (int e = 0; e < g.nsweeps; ++e) {
-        if (!mbar_wait(&bars[BQ_AB_FULL], e & 1, abort_flag)) return ERR_BQ_MMA;
+        if (!mbar_wait(&bars[BQ_AB_FULL], e & 1, abort_flag, 0, 1)) return ERR_BQ_MMA;
         for (int w = 0; w < g.nunits; ++w, ++u) {
             const int half = u & 1;
             if constexpr (D == 64) {
                 // the buffer holds P / G of this half's previous unit until its U / W products are done
-                if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
+                if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
             } else {
                 // the unit lands in slot `half` after the U / W products of the slot's previous unit are done
-                if (!mbar_wait(&bars[BQ_KV_SLOT + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_MMA;
+                if (!mbar_wait(&bars[BQ_KV_SLOT + half], (u >> 1) & 1, abort_flag, 0, 3)) return ERR_BQ_MMA;
             }
             tc_fence_after();
             const uint32_t d = tmem + half * 128 + which * 64;
@@ -294,7 +282,7 @@ __device__ __forceinline__ int bq_ring_producer(const BqParams &P, const BqGeom 
     int w = 0;
     for (int u = 0; u < g.total; ++u) {
         const int half = u & 1;
-        if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag, 32)) return ERR_BQ_PRODUCER;
+        if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag, 32, 1)) return ERR_BQ_PRODUCER;
         const int row = g.ubase + 64 * w;
         mbar_arrive_expect_tx(&bars[BQ_KV_SLOT + half], 4 * C::UBLK);
 #pragma unroll
@@ -337,8 +325,8 @@ __device__ __forceinline__ int bq_mma_second(const BqParams &P, const BqGeom &g,
         const int wb = e & 1;
         for (int w = 0; w < g.nunits; ++w, ++u) {
             const int half = u & 1;
-            if (!mbar_wait(&bars[BQ_P_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_MMA;
-            if (w == 0 && e >= 2 && !mbar_wait(&bars[BQ_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag)) return ERR_BQ_MMA;
+            if (!mbar_wait(&bars[BQ_P_FULL + half], (u >> 1) & 1, abort_flag, 0, 1)) return ERR_BQ_MMA;
+            if (w == 0 && e >= 2 && !mbar_wait(&bars[BQ_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
             tc_fence_after();
             const uint64_t off = (uint64_t)((D == 64 ? w * 8192 : half * 2 * C::UBLK) >> 4);
             const uint64_t kt = dK + off, vt = dV + off;
@@ -386,7 +374,7 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
                 const int d1 = i + kp.off1 - j0;
                 const int hi = sweep_ok ? min(d1, 63) : -1;         // valid columns: lo < col <= hi
                 const int lo = max(d1 - kp.w1, -j0 - 1);
-                if (!warp_wait(&bars[BQ_S_FULL + half], (u >> 1) & 1, abort_flag)) return ERR_BQ_COMPUTE;
+                if (!warp_wait(&bars[BQ_S_FULL + half], (u >> 1) & 1, abort_flag, 1)) return ERR_BQ_COMPUTE;
                 tc_fence_after();
                 const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
 #pragma unroll
@@ -435,8 +423,42 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
 // ---------------------------------------------------------------- fold (warps 8-11): U, W -> dQ, dK2, dV2
 __device__ __forceinline__ void bq_fold_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// Head dim 128: the fold thread of query row r forms row r of B_e = dO_i * v2_{i-e} for sweep e (the builder
+// group forms A_e), 64 channels at a time; the first 64 are fetched before the wait for the stage.
 template <int D>
-__device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
+__device__ __forceinline__ bool bq_build_b(const BqParams &P, const BqGeom &g, int e, int r, uint8_t *sB, uint64_t *bars,
+                                           volatile int *abort_flag) {
+    const KernelParams &kp = P.kp;
+    const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
+    const int i = g.i0 + r;
+    const int kk = i + kp.off2 - e;
+    const bool ok = i < kp.n && kk >= 0;
+    const __nv_bfloat16 *dp = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, ok ? i : 0, h);
+    const __nv_bfloat16 *vp = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p) + elem_off(kp.v2, b, ok ? kk : 0, hk);
+#pragma unroll
+    for (int cb = 0; cb < 2; ++cb) {
+        uint4 dv[8], vv[8];
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+            dv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(dp + cb * 64 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            vv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(vp + cb * 64 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (cb == 0 && e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag, 3)) return false;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+            uint4 bb;
+            bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
+            bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
+            *reinterpret_cast<uint4 *>(sB + cb * BqCfg<D>::BLK + sw128_offset(r, cc)) = bb;
+        }
+    }
+    fence_proxy_async_smem();
+    mbar_arrive(&bars[BQ_AB_FULL]);
+    return true;
+}
+
+template <int D>
+__device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v, uint8_t *sB,
                                             uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -455,7 +477,7 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 
     auto drain = [&](int v) -> bool {
         const int wb = v & 1, e = v;
-        if (!warp_wait(&bars[BQ_W_FULL + wb], (v >> 1) & 1, abort_flag)) return false;
+        if (!warp_wait(&bars[BQ_W_FULL + wb], (v >> 1) & 1, abort_flag, 1)) return false;
         tc_fence_after();
         const int kk = i + kp.off2 - e;
         const bool ok = row_ok && kk >= 0;
@@ -522,11 +544,18 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 
     const int nv = g.total > 0 ? g.nsweeps : 0;       // a split whose tiles all lie before the sequence start has no work
     int err = 0;
+    if constexpr (D == 128) {
+        if (nv > 0 && !bq_build_b<D>(P, g, 0, r, sB, bars, abort_flag)) err = ERR_BQ_COMPUTE;
+    }
     for (int v = 0; v < nv && err == 0; ++v) {
+        if constexpr (D == 128) {
+            // B_e of the next sweep first: the tensor cores wait for it, U / W of this sweep have a buffer's slack
+            if (v + 1 < nv && !bq_build_b<D>(P, g, v + 1, r, sB, bars, abort_flag)) { err = ERR_BQ_COMPUTE; break; }
+        }
         if (!drain(v)) err = ERR_BQ_COMPUTE;
         // A row of the shared accumulators is written by thread r in this sweep and by another thread in
         // the next: every fold thread must have finished this one (all have arrived on W_EMPTY) first.
-        else if (!warp_wait(&bars[BQ_W_EMPTY + (v & 1)], (v >> 1) & 1, abort_flag)) err = ERR_BQ_COMPUTE;
+        else if (!warp_wait(&bars[BQ_W_EMPTY + (v & 1)], (v >> 1) & 1, abort_flag, 2)) err = ERR_BQ_COMPUTE;
     }
 
     // partial dQ of this split (NaN when a wait ran out, so that the failure is visible in the result)
@@ -542,7 +571,7 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 }
 
 template <int D>
-__device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v,
+__device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v, uint8_t *sB,
                                        uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
     const int ft = threadIdx.x - 256;                 // 0..127 among the fold threads
@@ -551,7 +580,7 @@ __device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint3
     // zero the shared accumulators (acc_v follows acc_k); only this group touches them
     for (int x = ft; x < 2 * acc_rows * BQ_ACC_STRIDE; x += 128) acc_k[x] = 0.f;
     bq_fold_sync();
-    const int err = bq_fold_body<D>(P, g, tmem, acc_k, acc_v, bars, abort_flag);
+    const int err = bq_fold_body<D>(P, g, tmem, acc_k, acc_v, sB, bars, abort_flag);
     // shared accumulators -> this CTA's 64 channels of its slab.  The barrier sits outside the body so
     // that a warp that gave up on a wait still reaches it.
     bq_fold_sync();
@@ -586,10 +615,11 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int x = 0; x < BQ_BAR_COUNT; ++x) {
-            const bool many = x == BQ_AB_FULL || (x >= BQ_P_FULL && x < BQ_P_FULL + 2) || (x >= BQ_W_EMPTY && x < BQ_W_EMPTY + 2);
+            const bool many = (x >= BQ_P_FULL && x < BQ_P_FULL + 2) || (x >= BQ_W_EMPTY && x < BQ_W_EMPTY + 2);
             // S_FULL and AB_EMPTY collect one commit from each of the two first-product issuers
             const bool two = (x >= BQ_S_FULL && x < BQ_S_FULL + 2) || x == BQ_AB_EMPTY;
-            mbar_init(&bars[x], many ? 128u : two ? 2u : 1u);
+            // head dim 64: the builders form A_e and B_e; head dim 128: the builders A_e, the fold group B_e
+            mbar_init(&bars[x], x == BQ_AB_FULL ? (D == 128 ? 256u : 128u) : many ? 128u : two ? 2u : 1u);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -605,6 +635,9 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     const BqGeom g = bq_geom<D>(P);
 
     int err = 0;
+#ifdef SA2_PROF
+    const long long prof_t0 = clock64();
+#endif
     if (warp < 4) {
         reg_dealloc<BQ_REGS_ISSUE>();                 // one instruction for the whole warpgroup
         if (warp == 0) {
@@ -623,12 +656,13 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
         err = bq_compute<D>(P, g, tmem, bars, abort_flag);
     } else if (warp < 12) {
         reg_alloc<BQ_REGS_FOLD>();
-        err = bq_fold<D>(P, g, tmem, acc_k, acc_v, bars, abort_flag);
+        err = bq_fold<D>(P, g, tmem, acc_k, acc_v, sB, bars, abort_flag);
     } else {
         reg_alloc<BQ_REGS_BUILD>();
         if (g.total > 0) err = bq_builder<D>(P, g, sA, sB, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
+    SA2_PROF_ADD(0, clock64() - prof_t0);
 
     tc_fence_before();
     __syncthreads();

@@ -122,8 +122,8 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
 
 // every lane of the warp waits; the result is uniform so that the .sync.aligned
 // tcgen05 instructions that follow are never reached by a partial warp
-__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, 64));
+__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int prof = -1) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, 64, prof));
 }
 
 struct FwdGeom {
@@ -289,7 +289,7 @@ __device__ __forceinline__ int fwd_softmax(const FwdParams &P, const FwdGeom &g,
             const int d1 = i + kp.off1 - j0;
             const int hi = sweep_ok ? min(d1, 63) : -1;
             const int lo = max(d1 - kp.w1, -j0 - 1);
-            if (!warp_wait(&bars[BAR_S_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
+            if (!warp_wait(&bars[BAR_S_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag, 1)) return ERR_FWD_SOFTMAX;
             tc_fence_after();
             const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
 
@@ -518,6 +518,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
     const FwdGeom g = fwd_geom(P);
 
     int err = 0;
+#ifdef SA2_PROF
+    const long long prof_t0 = clock64();
+#endif
     if (warp < 4) {
         reg_dealloc<FWD_REGS_ISSUE>();                // one instruction for the whole warpgroup
         if ((threadIdx.x & 31) == 0) {
@@ -574,6 +577,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUt
         }
     }
     if (err) atomicOr(P.status, err);
+    SA2_PROF_ADD(0, clock64() - prof_t0);
 
     tc_fence_before();
     __syncthreads();

@@ -30,14 +30,15 @@
 //     reported; a sweep whose reference is lower is scaled down while it is
 //     folded in.
 //
-// Warps (640 threads, five aligned warpgroups):
-//   0      lane 0 issues the tcgen05.mma stream of group 1
-//   1      owns the TMEM allocation; lane 0 issues the stream of group 0
-//   2      lane 0 is the TMA producer of the K1 ring
-//   3      lane 0 is the TMA producer of the V1 ring
+// Warps (768 threads, six aligned warpgroups):
+//   0, 1   lane 0 issues the S products of group 0 / group 1 (warp 1 owns the TMEM allocation)
+//   2, 3   lane 0 issues the P V1 products of group 0 / group 1.  A thread issues one tcgen05
+//          instruction per 60-130 cycles and a unit takes 12 products and 6 commits, so with one
+//          issuing thread per group the issue itself (~3900 cycles per unit) paced the kernel.
 //   4-7    output threads of channel block 0, one per query row
 //   8-11   output threads of channel block 1
 //   12-15  softmax group 0 (even sweeps), 16-19 softmax group 1 (odd sweeps)
+//   20, 21 lane 0 is the TMA producer of the K1 ring / of the V1 ring; 22-23 idle
 #pragma once
 #include "sa2_tc_fwd.cuh"
 
@@ -45,10 +46,13 @@ namespace sa2 {
 namespace tc {
 namespace f128 {
 
-constexpr int THREADS = 640;
-// 640 threads start with 96 registers each; the budgets must add up to at most 5 * 96.
-constexpr int REGS_LAUNCH = 96, REGS_ISSUE = 32, REGS_OUT = 128, REGS_SOFTMAX = REGS_LAUNCH;
-static_assert(REGS_ISSUE + 2 * REGS_OUT + 2 * REGS_SOFTMAX <= 5 * REGS_LAUNCH, "register pool must balance");
+constexpr int THREADS = 768;
+// 768 threads start with 80 registers each; every warpgroup executes one setmaxnreg, and the budgets must add
+// up to at most 6 * 80 or the growing groups never return from theirs.
+constexpr int REGS_LAUNCH = 80, REGS_ISSUE = 56, REGS_OUT = 128, REGS_SOFTMAX = 72, REGS_PRODUCE = 24;
+static_assert(REGS_ISSUE + 2 * REGS_OUT + 2 * REGS_SOFTMAX + REGS_PRODUCE <= 6 * REGS_LAUNCH, "register pool must balance");
+static_assert(REGS_ISSUE <= REGS_LAUNCH && REGS_SOFTMAX <= REGS_LAUNCH && REGS_PRODUCE <= REGS_LAUNCH && REGS_OUT >= REGS_LAUNCH,
+              "issuers, softmax groups and producers release registers, the output groups take them");
 
 constexpr int UNIT = 64;                          // first-key rows per unit
 constexpr int SLOTS = 4;                          // slots of the K1 ring and of the V1 ring
@@ -114,7 +118,7 @@ __device__ __forceinline__ int producer(const Params &P, const Geom &g, const CU
     int w = 0;
     for (int x = 0; x < items; ++x) {
         const int slot = x % SLOTS;
-        if (x >= SLOTS && !mbar_wait(&bars[empty0 + slot], (x / SLOTS - 1) & 1, abort_flag, 32)) return ERR_FWD_PRODUCER;
+        if (x >= SLOTS && !mbar_wait(&bars[empty0 + slot], (x / SLOTS - 1) & 1, abort_flag, 32, 1)) return ERR_FWD_PRODUCER;
         const int row = g.hbase + UNIT * (g.h_first + w);
         mbar_arrive_expect_tx(&bars[full0 + slot], UNIT_BYTES);
         tma_load_4d(ring + slot * UNIT_BYTES, map, &bars[full0 + slot], 0, hk, row, b);
@@ -127,30 +131,25 @@ __device__ __forceinline__ int producer(const Params &P, const Geom &g, const CU
     return 0;
 }
 
-// ------------------------------------------------------------------ MMA issuers (one lane per group)
-// Group g's stream: unit r is unit r % nunits of the group's (r / nunits)-th sweep, e = 2 (r / nunits) + g,
-// in ring slot r % SLOTS.  Buffer r & 1 of the group holds S, then P, of unit r.
-__device__ __forceinline__ int mma_stream(const Params &P, const Geom &g, int grp, uint32_t tmem, uint8_t *sK, uint8_t *sV,
-                                          uint8_t *sA, uint64_t *bars, volatile int *abort_flag) {
+// ------------------------------------------------------------------ MMA issuers (two lanes per group)
+// Group g's units: unit r is unit r % nunits of the group's (r / nunits)-th sweep, e = 2 (r / nunits) + g,
+// in ring slot r % SLOTS.  Buffer r & 1 of the group holds S, then P, of unit r.  The S products and the
+// P V1 products of a group are issued by two threads; everything that orders them goes through barriers.
+__device__ __forceinline__ int issue_s(const Params &P, const Geom &g, int grp, uint32_t tmem, uint8_t *sK, uint8_t *sA,
+                                       uint64_t *bars, volatile int *abort_flag) {
     constexpr uint32_t IDESC_S = idesc_bf16(128, 64, false, false);
-    constexpr uint32_t IDESC_PV = idesc_bf16(128, 128, false, true);
-    constexpr uint32_t IDESC_PV64 = idesc_bf16(128, 64, false, true);
     const uint64_t dA = smem_desc_sw128(smem_u32(sA) + grp * A_BYTES);
     const uint64_t dK = smem_desc_sw128(smem_u32(sK));
-    const uint64_t dV = smem_desc_sw128(smem_u32(sV), 1024, BLK_BYTES);     // N = 128: channel blocks 8 KB apart
-    const uint32_t tS = tmem + grp * 128, tW = tmem + 256 + grp * 128;
+    const uint32_t tS = tmem + grp * 128;
     const int nu = g.nunits;
     const int n = g.nsw[grp] * nu;
-    int u_s = 0, u_p = 0;      // units whose S / PV have been issued so far
-    int s_w = 0, p_w = 0;      // their position within the sweep
-    int ks_s = 0, ks_p = 0;    // sweeps whose S / PV streams have started
-
-    auto issue_s = [&]() -> bool {
-        const int sb = u_s & 1, slot = u_s % SLOTS;
-        if (s_w == 0 && !mbar_wait(&bars[B_A_FULL + grp], ks_s & 1, abort_flag)) return false;
-        if (!mbar_wait(&bars[B_K_FULL + slot], (u_s / SLOTS) & 1, abort_flag)) return false;
+    int w = 0, ks = 0;
+    for (int u = 0; u < n; ++u) {
+        const int sb = u & 1, slot = u % SLOTS;
+        if (w == 0 && !mbar_wait(&bars[B_A_FULL + grp], ks & 1, abort_flag, 0, 1)) return ERR_FWD_MMA;
+        if (!mbar_wait(&bars[B_K_FULL + slot], (u / SLOTS) & 1, abort_flag, 0, 2)) return ERR_FWD_MMA;
         // P of the unit that used this buffer last must have been consumed: S overwrites it
-        if (u_s >= 2 && !mbar_wait(&bars[B_PV_DONE + grp * 2 + sb], ((u_s - 2) >> 1) & 1, abort_flag)) return false;
+        if (u >= 2 && !mbar_wait(&bars[B_PV_DONE + grp * 2 + sb], ((u - 2) >> 1) & 1, abort_flag, 0, 3)) return ERR_FWD_MMA;
         tc_fence_after();
         const uint64_t kt = dK + (uint64_t)((slot * UNIT_BYTES) >> 4);
         const uint32_t d = tS + sb * 64;
@@ -162,42 +161,8 @@ __device__ __forceinline__ int mma_stream(const Params &P, const Geom &g, int gr
         }
         tc_commit(&bars[B_S_FULL + grp * 2 + sb]);
         tc_commit(&bars[B_K_EMPTY + slot]);
-        if (s_w == nu - 1) tc_commit(&bars[B_A_FREE + grp]);      // the A stage may be rebuilt
-        ++u_s;
-        if (++s_w == nu) { s_w = 0; ++ks_s; }
-        return true;
-    };
-    auto issue_pv = [&]() -> bool {
-        const int sb = u_p & 1, slot = u_p % SLOTS;
-        if (!mbar_wait(&bars[B_V_FULL + slot], (u_p / SLOTS) & 1, abort_flag)) return false;
-        if (!mbar_wait(&bars[B_P_FULL + grp * 2 + sb], (u_p >> 1) & 1, abort_flag)) return false;
-        if (p_w == 0 && ks_p >= 1 && !mbar_wait(&bars[B_W_EMPTY + grp], (ks_p - 1) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t a = tS + sb * 64;                 // P lies over the first 32 columns of its S
-        const uint64_t vt = dV + (uint64_t)((slot * UNIT_BYTES) >> 4);
-        if (!P.pv_split) {
-#pragma unroll
-            for (int st = 0; st < 4; ++st) mma_ts(tW, a + st * 8, vt + st * 128, IDESC_PV, (p_w > 0 || st > 0) ? 1u : 0u);
-        } else {
-#pragma unroll
-            for (int st = 0; st < 4; ++st) {
-                mma_ts(tW, a + st * 8, vt + st * 128, IDESC_PV64, (p_w > 0 || st > 0) ? 1u : 0u);
-                mma_ts(tW + 64, a + st * 8, vt + (BLK_BYTES >> 4) + st * 128, IDESC_PV64, (p_w > 0 || st > 0) ? 1u : 0u);
-            }
-        }
-        tc_commit(&bars[B_PV_DONE + grp * 2 + sb]);
-        tc_commit(&bars[B_V_EMPTY + slot]);
-        if (p_w == nu - 1) tc_commit(&bars[B_W_FULL + grp]);
-        ++u_p;
-        if (++p_w == nu) { p_w = 0; ++ks_p; }
-        return true;
-    };
-
-    for (int r = 0; r < 2 && r < n; ++r)
-        if (!issue_s()) return ERR_FWD_MMA;
-    for (int r = 0; r < n; ++r) {
-        if (!issue_pv()) return ERR_FWD_MMA;
-        if (r + 2 < n && !issue_s()) return ERR_FWD_MMA;
+        if (w == nu - 1) tc_commit(&bars[B_A_FREE + grp]);      // the A stage may be rebuilt
+        if (++w == nu) { w = 0; ++ks; }
     }
     // The rings follow group 0's walk.  With an odd number of sweeps group 1 has one sweep less: it lets the
     // units of that last sweep pass, so that every slot still collects two releases.
@@ -205,6 +170,44 @@ __device__ __forceinline__ int mma_stream(const Params &P, const Geom &g, int gr
         const int slot = x % SLOTS;
         if (!mbar_wait(&bars[B_K_FULL + slot], (x / SLOTS) & 1, abort_flag, 32)) return ERR_FWD_MMA;
         mbar_arrive(&bars[B_K_EMPTY + slot]);
+    }
+    return 0;
+}
+
+__device__ __forceinline__ int issue_pv(const Params &P, const Geom &g, int grp, uint32_t tmem, uint8_t *sV,
+                                        uint64_t *bars, volatile int *abort_flag) {
+    constexpr uint32_t IDESC_PV = idesc_bf16(128, 128, false, true);
+    constexpr uint32_t IDESC_PV64 = idesc_bf16(128, 64, false, true);
+    const uint64_t dV = smem_desc_sw128(smem_u32(sV), 1024, BLK_BYTES);     // N = 128: channel blocks 8 KB apart
+    const uint32_t tS = tmem + grp * 128, tW = tmem + 256 + grp * 128;
+    const int nu = g.nunits;
+    const int n = g.nsw[grp] * nu;
+    int w = 0, ks = 0;
+    for (int u = 0; u < n; ++u) {
+        const int sb = u & 1, slot = u % SLOTS;
+        if (!mbar_wait(&bars[B_V_FULL + slot], (u / SLOTS) & 1, abort_flag, 0, 4)) return ERR_FWD_MMA;
+        if (!mbar_wait(&bars[B_P_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag, 0, 5)) return ERR_FWD_MMA;
+        if (w == 0 && ks >= 1 && !mbar_wait(&bars[B_W_EMPTY + grp], (ks - 1) & 1, abort_flag, 0, 6)) return ERR_FWD_MMA;
+        tc_fence_after();
+        const uint32_t a = tS + sb * 64;                 // P lies over the first 32 columns of its S
+        const uint64_t vt = dV + (uint64_t)((slot * UNIT_BYTES) >> 4);
+        if (!P.pv_split) {
+#pragma unroll
+            for (int st = 0; st < 4; ++st) mma_ts(tW, a + st * 8, vt + st * 128, IDESC_PV, (w > 0 || st > 0) ? 1u : 0u);
+        } else {
+#pragma unroll
+            for (int st = 0; st < 4; ++st) {
+                mma_ts(tW, a + st * 8, vt + st * 128, IDESC_PV64, (w > 0 || st > 0) ? 1u : 0u);
+                mma_ts(tW + 64, a + st * 8, vt + (BLK_BYTES >> 4) + st * 128, IDESC_PV64, (w > 0 || st > 0) ? 1u : 0u);
+            }
+        }
+        tc_commit(&bars[B_PV_DONE + grp * 2 + sb]);
+        tc_commit(&bars[B_V_EMPTY + slot]);
+        if (w == nu - 1) tc_commit(&bars[B_W_FULL + grp]);
+        if (++w == nu) { w = 0; ++ks; }
+    }
+    for (int x = n; x < g.nsw[0] * nu; ++x) {
+        const int slot = x % SLOTS;
         if (!mbar_wait(&bars[B_V_FULL + slot], (x / SLOTS) & 1, abort_flag, 32)) return ERR_FWD_MMA;
         mbar_arrive(&bars[B_V_EMPTY + slot]);
     }
@@ -228,6 +231,9 @@ __device__ __forceinline__ int softmax(const Params &P, const Geom &g, int grp, 
     float ref = -CUDART_INF_F, l = 0.f;
     int u = 0;
     const int nu = g.nunits;
+    // The hand-over of a unit's P (wait for the TMEM stores, then arrive) is deferred until the first load of
+    // the next unit has been issued, so that the store latency passes under that load.
+    int pending = -1;
     {
         for (int ks = 0; ks < nsw; ++ks) {
             const int e = 2 * ks + grp;
@@ -240,7 +246,7 @@ __device__ __forceinline__ int softmax(const Params &P, const Geom &g, int grp, 
                 const int d1 = i + kp.off1 - j0;
                 const int hi = sweep_ok ? min(d1, 63) : -1;
                 const int lo = max(d1 - kp.w1, -j0 - 1);
-                if (!warp_wait(&bars[B_S_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
+                if (!warp_wait(&bars[B_S_FULL + grp * 2 + sb], (u >> 1) & 1, abort_flag, 1)) return ERR_FWD_SOFTMAX;
                 tc_fence_after();
                 const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
                 const uint32_t buf = s_addr + sb * 64;
@@ -248,6 +254,12 @@ __device__ __forceinline__ int softmax(const Params &P, const Geom &g, int grp, 
                 // the whole unit is read before any P is stored: P lies over the S columns
                 uint32_t s[32], pk0[16], pk1[16];
                 tmem_ld32(buf, s);
+                if (pending >= 0) {
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&bars[B_P_FULL + grp * 2 + pending]);
+                    pending = -1;
+                }
                 tmem_wait_ld();
                 float tile_sum = fwd_probs32(s, pk0, c, ref, full, 0, lo, hi);
                 tmem_ld32(buf + 32, s);
@@ -298,20 +310,23 @@ __device__ __forceinline__ int softmax(const Params &P, const Geom &g, int grp, 
                 l += tile_sum;
                 tmem_st16(buf, pk0);
                 tmem_st16(buf + 16, pk1);
-                tmem_wait_st();
+                pending = sb;
                 if (w == nu - 1) {
                     // W of this sweep is expressed against the reference the row has now.  The output
                     // threads have read the slot of two sweeps ago before they released that sweep's W;
                     // waiting for the release of the previous one also keeps this barrier from running two
                     // phases ahead of its readers.
-                    if (ks >= 1 && !warp_wait(&bars[B_W_EMPTY + grp], (ks - 1) & 1, abort_flag)) return ERR_FWD_SOFTMAX;
+                    if (ks >= 1 && !warp_wait(&bars[B_W_EMPTY + grp], (ks - 1) & 1, abort_flag, 2)) return ERR_FWD_SOFTMAX;
                     ref_slot[(ks & 1) * 128] = ref;
                     mbar_arrive(&bars[B_REF_FULL + grp]);
                 }
-                tc_fence_before();
-                mbar_arrive(&bars[B_P_FULL + grp * 2 + sb]);
             }
         }
+    }
+    if (pending >= 0) {
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars[B_P_FULL + grp * 2 + pending]);
     }
     stats[512 + grp * 128 + r] = l;
     stats[768 + grp * 128 + r] = ref;
@@ -359,7 +374,7 @@ __device__ __forceinline__ int output(const Params &P, const Geom &g, int cb, ui
                 qv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(qrow + (half * 4 + cc) * 8)) : make_uint4(0u, 0u, 0u, 0u);
                 kv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(krow + (half * 4 + cc) * 8)) : make_uint4(0u, 0u, 0u, 0u);
             }
-            if (half == 0 && bar && !warp_wait(bar, parity, abort_flag)) return false;
+            if (half == 0 && bar && !warp_wait(bar, parity, abort_flag, 1)) return false;
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
                 uint4 v;
@@ -382,9 +397,9 @@ __device__ __forceinline__ int output(const Params &P, const Geom &g, int cb, ui
         uint4 raw[8];
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) raw[cc] = row ? __ldg(reinterpret_cast<const uint4 *>(vp + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
-        if (!warp_wait(&bars[B_REF_FULL + grp], t & 1, abort_flag)) return false;
+        if (!warp_wait(&bars[B_REF_FULL + grp], t & 1, abort_flag, 2)) return false;
         const float ref_w = stats[grp * 256 + (t & 1) * 128 + r];
-        if (!warp_wait(&bars[B_W_FULL + grp], t & 1, abort_flag)) return false;
+        if (!warp_wait(&bars[B_W_FULL + grp], t & 1, abort_flag, 3)) return false;
         tc_fence_after();
         const bool ok = row && ref_w > -CUDART_INF_F;
         float fw = 1.f;
@@ -474,17 +489,25 @@ fwd128_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     const uint32_t tmem = *tmem_holder;
 
     int err = 0;
+#ifdef SA2_PROF
+    const long long prof_t0 = clock64();
+#endif
     if (warp < 4) {
         reg_dealloc<REGS_ISSUE>();                    // one instruction for the whole warpgroup
         if ((threadIdx.x & 31) == 0) {
-            if (warp == 0) err = mma_stream(P, g, 1, tmem, sK, sV, sA, bars, abort_flag);
-            else if (warp == 1) err = mma_stream(P, g, 0, tmem, sK, sV, sA, bars, abort_flag);
-            else if (warp == 2) err = producer(P, g, &mapK, sK, B_K_FULL, B_K_EMPTY, bars, abort_flag);
-            else err = producer(P, g, &mapV, sV, B_V_FULL, B_V_EMPTY, bars, abort_flag);
+            if (warp < 2) err = issue_s(P, g, warp, tmem, sK, sA, bars, abort_flag);
+            else err = issue_pv(P, g, warp - 2, tmem, sV, bars, abort_flag);
+        }
+        __syncwarp();
+    } else if (warp >= 20) {
+        reg_dealloc<REGS_PRODUCE>();
+        if ((threadIdx.x & 31) == 0) {
+            if (warp == 20) err = producer(P, g, &mapK, sK, B_K_FULL, B_K_EMPTY, bars, abort_flag);
+            else if (warp == 21) err = producer(P, g, &mapV, sV, B_V_FULL, B_V_EMPTY, bars, abort_flag);
         }
         __syncwarp();
     } else if (warp >= 12) {
-        // the softmax groups keep the 96 registers every thread starts with
+        reg_dealloc<REGS_SOFTMAX>();
         err = softmax(P, g, (warp - 12) >> 2, tmem, stats, bars, abort_flag);
         // the barrier sits outside softmax() so that a group that gave up still reaches it
         rows_sync();
@@ -527,6 +550,7 @@ fwd128_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
         }
     }
     if (err) atomicOr(P.status, err);
+    SA2_PROF_ADD(0, clock64() - prof_t0);
 
     tc_fence_before();
     __syncthreads();
