@@ -183,6 +183,15 @@ int sa2_device_status(int reset);
  */
 int sa2_check_device(int reset);
 
+/*
+ * Self-test of the bounded waits: launches one warp that waits, for at most `limit_cycles` SM clock
+ * cycles (1 ... 2e9), on a barrier nobody arrives on.  The wait runs out, the kernel sets
+ * SA2_SELFTEST_WAIT_BIT in the device status word and ends normally - nothing faults or hangs.
+ * sa2_check_device() then reports SA2_ERR_DEVICE once.  No counterpart in the reference.
+ */
+#define SA2_SELFTEST_WAIT_BIT 0x10000
+int sa2_selftest_wait(long long limit_cycles, void *stream);
+
 /* Static, human-readable text for a status code. */
 const char *sa2_strerror(int status);
 

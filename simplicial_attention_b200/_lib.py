@@ -18,9 +18,12 @@ BWD_ROWSUM, BWD_K1, BWD_Q = 1, 2, 4     # sa2_bwd_phase
 
 # symbols declared in include/sa2.h
 EXPORTS = ("sa2_fwd", "sa2_bwd", "sa2_bwd_workspace_bytes", "sa2_strerror", "sa2_version",
-           "sa2_kernel_launches", "sa2_device_status", "sa2_check_device", "sa2_bwd_static_scratch",
+           "sa2_kernel_launches", "sa2_device_status", "sa2_check_device", "sa2_selftest_wait",
+           "sa2_bwd_static_scratch",
            "sa2_headnorm_fwd", "sa2_headnorm_bwd", "sa2_headnorm_partial_bytes")
 STATIC_SCRATCH_ROWS = 262144   # SA2_STATIC_SCRATCH_ROWS in include/sa2.h
+SELFTEST_WAIT_BIT = 0x10000    # SA2_SELFTEST_WAIT_BIT
+SA2_ERR_DEVICE = 5
 
 
 class Strides(C.Structure):
@@ -104,6 +107,8 @@ def lib() -> C.CDLL:
         handle.sa2_kernel_launches.restype = C.c_int
         handle.sa2_device_status.argtypes = [C.c_int]
         handle.sa2_device_status.restype = C.c_int
+        handle.sa2_selftest_wait.argtypes = [C.c_longlong, C.c_void_p]
+        handle.sa2_selftest_wait.restype = C.c_int
         handle.sa2_check_device.argtypes = [C.c_int]
         handle.sa2_check_device.restype = C.c_int
         handle.sa2_strerror.argtypes = [C.c_int]

@@ -5,6 +5,17 @@
 #include "sa2_simt.cuh"
 #include "sa2_tc.cuh"
 #include "sa2_headnorm.cuh"
+#include <nvtx3/nvToolsExt.h>
+
+namespace sa2 {
+namespace nvtx {
+// NVTX range around an entry point (header-only NVTX v3: a no-op unless a profiler is attached)
+struct Range {
+    explicit Range(const char *name) { nvtxRangePushA(name); }
+    ~Range() { nvtxRangePop(); }
+};
+}  // namespace nvtx
+}  // namespace sa2
 
 namespace {
 
@@ -86,11 +97,61 @@ int simt_bwd(const KernelParams &p, cudaStream_t st, int phases = 0) {
     return SA2_OK;
 }
 
+// argument checks shared by sa2_bwd and sa2_bwd_static_scratch
+int check_bwd_args(const sa2_bwd_args *a) {
+    if (!a) return SA2_ERR_INVALID;
+    if (int e = check_shape(a->shape)) return e;
+    if (!a->q || !a->k1 || !a->k2 || !a->v1 || !a->v2 || !a->out || !a->dout || !a->lse) return SA2_ERR_INVALID;
+    if (!a->dq || !a->dk1 || !a->dk2 || !a->dv1 || !a->dv2) return SA2_ERR_INVALID;
+    if (a->grad_dtype != SA2_F32 && a->grad_dtype != SA2_BF16) return SA2_ERR_UNSUPPORTED;
+    const void *ptrs[] = {a->q, a->k1, a->k2, a->v1, a->v2, a->out, a->dout, a->dq, a->dk1, a->dk2, a->dv1, a->dv2};
+    for (const void *p : ptrs) if (!aligned16(p)) return SA2_ERR_INVALID;
+    const sa2_strides *ss[] = {&a->sq, &a->sk1, &a->sk2, &a->sv1, &a->sv2, &a->sout, &a->sdout,
+                               &a->sdq, &a->sdk1, &a->sdk2, &a->sdv1, &a->sdv2};
+    for (const sa2_strides *s : ss) if (!strides_ok(*s)) return SA2_ERR_INVALID;
+    return SA2_OK;
+}
+
+void fill_bwd_params(KernelParams &p, const sa2_bwd_args *a, float *rowsum) {
+    fill_common(p, a->shape);
+    p.grad_bf16 = (a->grad_dtype == SA2_BF16);
+    p.q = ref(a->q, a->sq); p.k1 = ref(a->k1, a->sk1); p.k2 = ref(a->k2, a->sk2);
+    p.v1 = ref(a->v1, a->sv1); p.v2 = ref(a->v2, a->sv2);
+    p.out = ref(a->out, a->sout); p.dout = ref(a->dout, a->sdout);
+    p.dq = ref(a->dq, a->sdq); p.dk1 = ref(a->dk1, a->sdk1); p.dk2 = ref(a->dk2, a->sdk2);
+    p.dv1 = ref(a->dv1, a->sdv1); p.dv2 = ref(a->dv2, a->sdv2);
+    p.lse = const_cast<float *>(a->lse);
+    p.delta = rowsum;
+}
+
+// One block of one warp waits on a barrier that nobody arrives on, with the given limit: the self-test of
+// the bounded waits.  The wait runs out, the block records ERR_SELFTEST and leaves through the normal path.
+__global__ void selftest_wait_kernel(long long limit_cycles, int *status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        sa2::sm100::mbar_init(&bar, 1);
+        abort_flag = 0;
+        sa2::sm100::fence_barrier_init();
+    }
+    __syncthreads();
+    const bool ok = sa2::sm100::mbar_wait(&bar, 0, &abort_flag, 32, -1, limit_cycles);
+    if (!ok && threadIdx.x == 0) atomicOr(status, SA2_SELFTEST_WAIT_BIT);
+}
+
 }  // namespace
 
 extern "C" {
 
 int sa2_version(void) { return 100; }
+
+int sa2_selftest_wait(long long limit_cycles, void *stream) {
+    if (limit_cycles <= 0 || limit_cycles > 2000000000LL) return SA2_ERR_INVALID;
+    int *word = sa2::tc::status_word();
+    if (!word) return SA2_ERR_CUDA;
+    selftest_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(limit_cycles, word);
+    return launch_status();
+}
 
 #ifdef SA2_PROF
 // diagnostic builds only (-DSA2_PROF=<CTA index>): read and clear the wait-accounting table
@@ -150,6 +211,7 @@ size_t sa2_bwd_workspace_bytes(const sa2_shape *s) {
 }
 
 int sa2_fwd(const sa2_fwd_args *a) {
+    sa2::nvtx::Range range("sa2_fwd");
     if (!a) return SA2_ERR_INVALID;
     if (int e = check_shape(a->shape)) return e;
     if (!a->q || !a->k1 || !a->k2 || !a->v1 || !a->v2 || !a->out || !a->lse) return SA2_ERR_INVALID;
@@ -177,31 +239,15 @@ int sa2_fwd(const sa2_fwd_args *a) {
 }
 
 int sa2_bwd(const sa2_bwd_args *a) {
-    if (!a) return SA2_ERR_INVALID;
-    if (int e = check_shape(a->shape)) return e;
-    if (!a->q || !a->k1 || !a->k2 || !a->v1 || !a->v2 || !a->out || !a->dout || !a->lse) return SA2_ERR_INVALID;
-    if (!a->dq || !a->dk1 || !a->dk2 || !a->dv1 || !a->dv2) return SA2_ERR_INVALID;
-    if (a->grad_dtype != SA2_F32 && a->grad_dtype != SA2_BF16) return SA2_ERR_UNSUPPORTED;
+    sa2::nvtx::Range range("sa2_bwd");
+    if (int e = check_bwd_args(a)) return e;
     if (a->phases < 0 || a->phases > (SA2_BWD_ROWSUM | SA2_BWD_K1 | SA2_BWD_Q)) return SA2_ERR_INVALID;
-    const void *ptrs[] = {a->q, a->k1, a->k2, a->v1, a->v2, a->out, a->dout, a->dq, a->dk1, a->dk2, a->dv1, a->dv2};
-    for (const void *p : ptrs) if (!aligned16(p)) return SA2_ERR_INVALID;
-    const sa2_strides *ss[] = {&a->sq, &a->sk1, &a->sk2, &a->sv1, &a->sv2, &a->sout, &a->sdout,
-                               &a->sdq, &a->sdk1, &a->sdk2, &a->sdv1, &a->sdv2};
-    for (const sa2_strides *s : ss) if (!strides_ok(*s)) return SA2_ERR_INVALID;
     const size_t need = sa2_bwd_workspace_bytes(&a->shape);
     if (!a->workspace || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u))
         return SA2_ERR_WORKSPACE;
 
     KernelParams p{};
-    fill_common(p, a->shape);
-    p.grad_bf16 = (a->grad_dtype == SA2_BF16);
-    p.q = ref(a->q, a->sq); p.k1 = ref(a->k1, a->sk1); p.k2 = ref(a->k2, a->sk2);
-    p.v1 = ref(a->v1, a->sv1); p.v2 = ref(a->v2, a->sv2);
-    p.out = ref(a->out, a->sout); p.dout = ref(a->dout, a->sdout);
-    p.dq = ref(a->dq, a->sdq); p.dk1 = ref(a->dk1, a->sdk1); p.dk2 = ref(a->dk2, a->sdk2);
-    p.dv1 = ref(a->dv1, a->sdv1); p.dv2 = ref(a->dv2, a->sdv2);
-    p.lse = const_cast<float *>(a->lse);
-    p.delta = reinterpret_cast<float *>(a->workspace);
+    fill_bwd_params(p, a, reinterpret_cast<float *>(a->workspace));
     cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
 
     const bool tc_ok = sa2::tc::bwd_supported(a->shape) && sa2::tc::bwd_addressable(p);
@@ -254,16 +300,8 @@ float *static_rowsum_ptr() {
 }  // namespace
 
 int sa2_bwd_static_scratch(const sa2_bwd_args *a) {
-    if (!a) return SA2_ERR_INVALID;
-    if (int e = check_shape(a->shape)) return e;
-    if (!a->q || !a->k1 || !a->k2 || !a->v1 || !a->v2 || !a->out || !a->dout || !a->lse) return SA2_ERR_INVALID;
-    if (!a->dq || !a->dk1 || !a->dk2 || !a->dv1 || !a->dv2) return SA2_ERR_INVALID;
-    if (a->grad_dtype != SA2_F32 && a->grad_dtype != SA2_BF16) return SA2_ERR_UNSUPPORTED;
-    const void *ptrs[] = {a->q, a->k1, a->k2, a->v1, a->v2, a->out, a->dout, a->dq, a->dk1, a->dk2, a->dv1, a->dv2};
-    for (const void *p : ptrs) if (!aligned16(p)) return SA2_ERR_INVALID;
-    const sa2_strides *ss[] = {&a->sq, &a->sk1, &a->sk2, &a->sv1, &a->sv2, &a->sout, &a->sdout,
-                               &a->sdq, &a->sdk1, &a->sdk2, &a->sdv1, &a->sdv2};
-    for (const sa2_strides *s : ss) if (!strides_ok(*s)) return SA2_ERR_INVALID;
+    sa2::nvtx::Range range("sa2_bwd_static_scratch");
+    if (int e = check_bwd_args(a)) return e;
     // only the fp32 kernels get by with the row sums alone
     if (a->shape.kernel == SA2_KERNEL_TCGEN05) return SA2_ERR_UNSUPPORTED;
     const long long rows = (long long)a->shape.b * a->shape.hq * a->shape.n;
@@ -273,15 +311,7 @@ int sa2_bwd_static_scratch(const sa2_bwd_args *a) {
     if (!rowsum) return SA2_ERR_CUDA;
 
     KernelParams p{};
-    fill_common(p, a->shape);
-    p.grad_bf16 = (a->grad_dtype == SA2_BF16);
-    p.q = ref(a->q, a->sq); p.k1 = ref(a->k1, a->sk1); p.k2 = ref(a->k2, a->sk2);
-    p.v1 = ref(a->v1, a->sv1); p.v2 = ref(a->v2, a->sv2);
-    p.out = ref(a->out, a->sout); p.dout = ref(a->dout, a->sdout);
-    p.dq = ref(a->dq, a->sdq); p.dk1 = ref(a->dk1, a->sdk1); p.dk2 = ref(a->dk2, a->sdk2);
-    p.dv1 = ref(a->dv1, a->sdv1); p.dv2 = ref(a->dv2, a->sdv2);
-    p.lse = const_cast<float *>(a->lse);
-    p.delta = rowsum;     // every entry the kernels read is rewritten first: nothing has to start at zero
+    fill_bwd_params(p, a, rowsum);    // every entry the kernels read is rewritten first: nothing has to start at zero
     cudaStream_t st = reinterpret_cast<cudaStream_t>(a->stream);
     switch (a->shape.d) {
         case 32: return simt_bwd<32>(p, st);
@@ -370,7 +400,13 @@ size_t sa2_headnorm_partial_bytes(int64_t rows, int32_t channels) {
     if (rows <= 0 || channels <= 0) return 0;
     return (size_t)headnorm_grid(rows) * (size_t)channels * sizeof(float);
 }
-int sa2_headnorm_fwd(const sa2_headnorm_args *a) { return headnorm_dispatch(a, false); }
-int sa2_headnorm_bwd(const sa2_headnorm_args *a) { return headnorm_dispatch(a, true); }
+int sa2_headnorm_fwd(const sa2_headnorm_args *a) {
+    sa2::nvtx::Range range("sa2_headnorm_fwd");
+    return headnorm_dispatch(a, false);
+}
+int sa2_headnorm_bwd(const sa2_headnorm_args *a) {
+    sa2::nvtx::Range range("sa2_headnorm_bwd");
+    return headnorm_dispatch(a, true);
+}
 
 }  // extern "C"

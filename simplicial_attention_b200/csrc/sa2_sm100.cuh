@@ -63,7 +63,7 @@ __device__ __forceinline__ void prof_add(int slot, long long cycles) {
 // `sleep_ns` > 0 makes the poller yield its issue slots between tries (used by
 // whole warps that wait; the single MMA-issuing lanes poll without sleeping).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned sleep_ns = 0,
-                                          int prof = -1) {
+                                          int prof = -1, long long limit_cycles = WAIT_LIMIT_CYCLES) {
 #ifdef SA2_PROF
     const long long t0 = clock64();       // a try_wait may suspend the thread: the first try counts as waiting too
     if (mbar_try_wait(bar, parity)) { SA2_PROF_ADD(prof, clock64() - t0); return true; }
@@ -76,7 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         if (sleep_ns) __nanosleep(sleep_ns);
         if ((++spins & 255) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (clock64() - t0 > limit_cycles) {
                 *abort_flag = 1;
                 return false;
             }

@@ -143,7 +143,7 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
                         tma_load_4d(sWin + BK1_WIN_ROWS * 128 + bx * 4096, mapV2, &bars[BK1_WIN_FULL], 0, hk, row0 + 32 * bx, b);
                     }
                 }
-                if (!mbar_wait(&bars[BK1_WIN_FULL], tile_counter & 1, abort_flag, 64)) return ERR_BK1_BUILDER;
+                if (!mbar_wait(&bars[BK1_WIN_FULL], tile_counter & 1, abort_flag, 64, 1)) return ERR_BK1_BUILDER;
             }
             uint4 qv[8], dv[8];
 #pragma unroll
@@ -163,7 +163,7 @@ __device__ __forceinline__ int bk1_builder(const BwdParams &P, const Bk1Geom &g,
             }
             for (int e = 0; e < ne; ++e, ++s) {
                 const int stage = s % BK1_STAGES;
-                if (s >= BK1_STAGES && !warp_wait(&bars[BK1_AB_EMPTY + stage], (s / BK1_STAGES - 1) & 1, abort_flag)) return ERR_BK1_BUILDER;
+                if (s >= BK1_STAGES && !warp_wait(&bars[BK1_AB_EMPTY + stage], (s / BK1_STAGES - 1) & 1, abort_flag, 2)) return ERR_BK1_BUILDER;
                 if (e == 0) {
                     // Statistics of this query tile: two K = 16 slabs (-lse2/c, -D) of a four-slab tile; two
                     // such tiles hold the last four query tiles.  Step s - 3 has completed, and every tile has
@@ -228,11 +228,11 @@ __device__ __forceinline__ int bk1_mma_first(const KernelParams &kp, const Bk1Ge
             const uint64_t stL0 = dSt + (uint64_t)((((tile_counter >> 1) & 1) * TILE_BYTES) >> 4) + (uint64_t)((tile_counter & 1) * 4);
             for (int e = 0; e < ne; ++e, ++s) {
                 const int stage = s % BK1_STAGES;
-                if (!mbar_wait(&bars[BK1_AB_FULL + stage], (s / BK1_STAGES) & 1, abort_flag)) return ERR_BK1_MMA;
+                if (!mbar_wait(&bars[BK1_AB_FULL + stage], (s / BK1_STAGES) & 1, abort_flag, 0, 1)) return ERR_BK1_MMA;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     // the compute group must have read the previous step's S^T / dP^T of this half
-                    if (s >= 1 && !mbar_wait(&bars[BK1_P_FULL + half], (s - 1) & 1, abort_flag)) return ERR_BK1_MMA;
+                    if (s >= 1 && !mbar_wait(&bars[BK1_P_FULL + half], (s - 1) & 1, abort_flag, 0, 2)) return ERR_BK1_MMA;
                     tc_fence_after();
                     const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4);
                     const uint64_t st = stL0 + (uint64_t)((half * 8192) >> 4) + (uint64_t)(which * 2);
@@ -258,7 +258,7 @@ __device__ __forceinline__ int bk1_mma_second(const Bk1Geom &g, uint32_t tmem, u
         const int stage = s % BK1_STAGES;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-            if (!mbar_wait(&bars[BK1_P_FULL + half], s & 1, abort_flag)) return ERR_BK1_MMA;
+            if (!mbar_wait(&bars[BK1_P_FULL + half], s & 1, abort_flag, 0, 1)) return ERR_BK1_MMA;
             tc_fence_after();
             const uint64_t a = dAB + (uint64_t)((stage * 2 * TILE_BYTES + half * 8192) >> 4), bq = a + (TILE_BYTES >> 4);
             const uint32_t t = tmem + 256 + half * 64;
@@ -303,11 +303,11 @@ __device__ __forceinline__ int bk1_compute(const BwdParams &P, const Bk1Geom &g,
                 const int hi = (jv ? min(min(TQ - 1, base + kp.w1 - 1), g.i_hi - it0) : -1) - half * 64;
                 for (int e = 0; e < ne; ++e, ++s) {
                     const int lo = max(max(0, base), e - kp.off2 - it0) - half * 64;     // valid columns: lo <= col <= hi
-                    if (!warp_wait(&bars[BK1_S_FULL + half], s & 1, abort_flag)) return ERR_BK1_COMPUTE;
+                    if (!warp_wait(&bars[BK1_S_FULL + half], s & 1, abort_flag, 1)) return ERR_BK1_COMPUTE;
                     tc_fence_after();
                     const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= 63);
                     // P^T / G^T of the previous step must have been consumed before they are overwritten
-                    if (s >= 1 && !warp_wait(&bars[BK1_G_DONE + half], (s - 1) & 1, abort_flag)) return ERR_BK1_COMPUTE;
+                    if (s >= 1 && !warp_wait(&bars[BK1_G_DONE + half], (s - 1) & 1, abort_flag, 2)) return ERR_BK1_COMPUTE;
 #pragma unroll
                     for (int ch = 0; ch < 2; ++ch) {
                         uint32_t sv[32], dv[32], pk[16], gk[16];
@@ -414,6 +414,9 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     const Bk1Geom g = bk1_geom(P.kp);
 
     int err = 0;
+#ifdef SA2_PROF
+    const long long prof_t0 = clock64();
+#endif
     if (warp == 0) {
         if (lane == 0) {
             if (g.total > 0) {
@@ -440,6 +443,7 @@ bwd_k1_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
         err = bk1_builder(P, g, &mapK2, &mapV2, sAB, sStat, sOnes, sWin, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
+    SA2_PROF_ADD(0, clock64() - prof_t0);
 
     tc_fence_before();
     __syncthreads();

@@ -189,7 +189,7 @@ __device__ __forceinline__ int fwd_mma(const FwdGeom &g, int grp, uint32_t tmem,
 
     auto issue_s = [&](int r) -> bool {
         const int tile = g.t_first + (s_w >> 1), half = s_w & 1, sb = r & 1;
-        if (s_w == 0 && !mbar_wait(&bars[BAR_A_FULL + grp], s_k & 1, abort_flag)) return false;
+        if (s_w == 0 && !mbar_wait(&bars[BAR_A_FULL + grp], s_k & 1, abort_flag, 0, 1)) return false;
         if (s_k == 0 && half == 0 && !mbar_wait(&bars[BAR_KV_FULL + tile], 0, abort_flag)) return false;
         tc_fence_after();
         const uint64_t kt = dK + (uint64_t)((tile * TILE_BYTES + half * 8192) >> 4);
@@ -205,8 +205,8 @@ __device__ __forceinline__ int fwd_mma(const FwdGeom &g, int grp, uint32_t tmem,
     };
     auto issue_pv = [&](int r) -> bool {
         const int tile = g.t_first + (p_w >> 1), half = p_w & 1, sb = r & 1;
-        if (!mbar_wait(&bars[BAR_P_FULL + grp * 2 + sb], (r >> 1) & 1, abort_flag)) return false;
-        if (p_w == 0 && p_k >= 1 && !mbar_wait(&bars[BAR_W_EMPTY + grp], (p_k - 1) & 1, abort_flag)) return false;
+        if (!mbar_wait(&bars[BAR_P_FULL + grp * 2 + sb], (r >> 1) & 1, abort_flag, 0, 2)) return false;
+        if (p_w == 0 && p_k >= 1 && !mbar_wait(&bars[BAR_W_EMPTY + grp], (p_k - 1) & 1, abort_flag, 0, 3)) return false;
         tc_fence_after();
         const uint64_t vt = dV + (uint64_t)((tile * TILE_BYTES + half * 8192) >> 4);
         const uint32_t a = tP + sb * 32;
@@ -422,9 +422,9 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
 
     // o += v2_{i-e} * W_e (TMEM), after moving o to the reference W_e was built against
     auto drain = [&](int grp, int k, float (&o)[64], float &ref_o) -> bool {
-        if (!warp_wait(&bars[BAR_REF_FULL + grp], k & 1, abort_flag)) return false;
+        if (!warp_wait(&bars[BAR_REF_FULL + grp], k & 1, abort_flag, 2)) return false;
         const float ref_w = stats[grp * 256 + (k & 1) * 128 + r];
-        if (!warp_wait(&bars[BAR_W_FULL + grp], k & 1, abort_flag)) return false;
+        if (!warp_wait(&bars[BAR_W_FULL + grp], k & 1, abort_flag, 3)) return false;
         tc_fence_after();
         const int kk = i + kp.off2 - (2 * k + grp);
         const bool ok = row_ok && kk >= 0 && ref_w > -CUDART_INF_F;
@@ -468,11 +468,11 @@ __device__ __forceinline__ int fwd_output(const FwdParams &P, const FwdGeom &g, 
     for (int k = 0; k < nsw0; ++k) {
         // the A stages first: the tensor cores wait for them, the W accumulators have a unit's slack
         if (k + 1 < nsw0) {
-            if (!warp_wait(&bars[BAR_A_FREE + 0], k & 1, abort_flag)) return ERR_FWD_OUTPUT;
+            if (!warp_wait(&bars[BAR_A_FREE + 0], k & 1, abort_flag, 1)) return ERR_FWD_OUTPUT;
             build_a(0, k + 1);
         }
         if (k + 1 < nsw1) {
-            if (!warp_wait(&bars[BAR_A_FREE + 1], k & 1, abort_flag)) return ERR_FWD_OUTPUT;
+            if (!warp_wait(&bars[BAR_A_FREE + 1], k & 1, abort_flag, 1)) return ERR_FWD_OUTPUT;
             build_a(1, k + 1);
         }
         if (!drain(0, k, o0, ref0)) return ERR_FWD_OUTPUT;

@@ -22,7 +22,10 @@ The reference is single-GPU; the operator shards in two ways:
 
   The kernels take the extended key tensors directly (their ``off1/off2``
   arguments) and write their results into views of the result tensors, so no
-  full-size tensor is copied or concatenated.
+  full-size tensor is copied or concatenated.  On CUDA the exchange and the
+  launches over the first r0 rows run on a side stream next to the interior
+  launches (they fill a fraction of one wave of CTAs; back to back on one stream
+  each of them would still cost a whole CTA's run time).
 
 No collective (all-reduce, all-gather) is needed for the operator itself.
 
@@ -114,6 +117,44 @@ class _Exchange:
         self.reqs = []
 
 
+_side_streams = {}
+
+
+class _Side:
+    """``with side:`` runs on a per-device side stream that starts after everything queued on the
+    current stream so far; ``side.join(*tensors)`` makes the current stream wait for it and tells the
+    allocator that the tensors made on the side stream are used on the current one.  A no-op for CPU
+    tensors."""
+
+    def __init__(self, ref: Tensor):
+        self.on = ref.is_cuda
+        if self.on:
+            dev = ref.device
+            if dev not in _side_streams:
+                _side_streams[dev] = torch.cuda.Stream(dev)
+            self.main, self.side = torch.cuda.current_stream(dev), _side_streams[dev]
+            self.side.wait_stream(self.main)
+            self.ctx = None
+
+    def __enter__(self):
+        if self.on:
+            self.ctx = torch.cuda.stream(self.side)
+            self.ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            self.ctx.__exit__(*exc)
+        return False
+
+    def join(self, *tensors):
+        if self.on:
+            self.main.wait_stream(self.side)
+            for t in tensors:
+                if t is not None and t.is_cuda:
+                    t.record_stream(self.main)
+
+
 def _cuda_forward(q, k1, k2, v1, v2, w1, w2, out=None, **kw):
     return sa2_forward(q, k1, k2, v1, v2, w1, w2, out=out, **kw)
 
@@ -142,22 +183,29 @@ class SequenceParallelAttention(Function):
         r0 = min(n, -(-max(h1, h2) // TILE) * TILE) if rank > 0 else 0
         ex = None
         halos = None
+        out = torch.empty_like(q)
+        lse_i = lse_b = None
+        send = recv = None
         if world > 1:
             send = [k1[:, n - h1:].contiguous(), v1[:, n - h1:].contiguous(),
                     k2[:, n - h2:].contiguous(), v2[:, n - h2:].contiguous()] if rank < world - 1 else None
             halos = [torch.empty_like(k1[:, :h1]), torch.empty_like(v1[:, :h1]),
                      torch.empty_like(k2[:, :h2]), torch.empty_like(v2[:, :h2])] if rank > 0 else None
-            ex = _Exchange(send, rank + 1, halos, rank - 1, group, "forward")
-        out = torch.empty_like(q)
-        lse_i = lse_b = None
+        side = _Side(q)
+        with side:
+            if world > 1:
+                ex = _Exchange(send, rank + 1, halos, rank - 1, group, "forward")
         if r0 < n:      # interior rows (all rows on rank 0): no halo needed
             _, lse_i = fwd(q[:, r0:], k1[:, r0 - h1 if rank > 0 else 0:], k2[:, r0 - h2 if rank > 0 else 0:],
                            v1[:, r0 - h1 if rank > 0 else 0:], v2[:, r0 - h2 if rank > 0 else 0:], w1, w2, out=out[:, r0:], **kw)
-        if ex is not None:
-            ex.wait(timeout, blocking)
-        if rank > 0:    # the first r0 rows against [halo | first r0 local rows]
-            ext = [torch.cat((h_, t[:, :r0]), dim=1) for h_, t in zip(halos, (k1, v1, k2, v2))]
-            _, lse_b = fwd(q[:, :r0], ext[0], ext[2], ext[1], ext[3], w1, w2, out=out[:, :r0], **kw)
+        ext = []
+        with side:
+            if ex is not None:
+                ex.wait(timeout, blocking)
+            if rank > 0:    # the first r0 rows against [halo | first r0 local rows]
+                ext = [torch.cat((h_, t[:, :r0]), dim=1) for h_, t in zip(halos, (k1, v1, k2, v2))]
+                _, lse_b = fwd(q[:, :r0], ext[0], ext[2], ext[1], ext[3], w1, w2, out=out[:, :r0], **kw)
+        side.join(lse_b, *ext)
         ctx.save_for_backward(q, k1, k2, v1, v2, out, lse_i, lse_b, *(halos or []))
         ctx.cfg = (w1, w2, group, engine, timeout, blocking, kw, rank, world, n, h1, h2, r0)
         return out
@@ -172,21 +220,28 @@ class SequenceParallelAttention(Function):
         dq, dk1, dk2, dv1, dv2 = grads
         ex = None
         bnd = None
-        if rank > 0:
-            # the first r0 rows first: their backward yields the gradient rows of the halo
-            ext = [torch.cat((h_, t[:, :r0]), dim=1) for h_, t in zip(halos, (k1, v1, k2, v2))]
-            bnd = bwd(q[:, :r0], ext[0], ext[2], ext[1], ext[3], out[:, :r0], lse_b, dout[:, :r0], w1, w2, **kw)
-        if world > 1:
-            send = [bnd[1][:, :h1].contiguous(), bnd[3][:, :h1].contiguous(),
-                    bnd[2][:, :h2].contiguous(), bnd[4][:, :h2].contiguous()] if rank > 0 else None
-            recv = [torch.empty_like(k1[:, :h1]), torch.empty_like(v1[:, :h1]),
-                    torch.empty_like(k2[:, :h2]), torch.empty_like(v2[:, :h2])] if rank < world - 1 else None
-            ex = _Exchange(send, rank - 1, recv, rank + 1, group, "backward")
+        ext, send = [], None
+        recv = [torch.empty_like(k1[:, :h1]), torch.empty_like(v1[:, :h1]),
+                torch.empty_like(k2[:, :h2]), torch.empty_like(v2[:, :h2])] if world > 1 and rank < world - 1 else None
+        side = _Side(q)
+        with side:
+            if rank > 0:
+                # the first r0 rows first: their backward yields the gradient rows of the halo
+                ext = [torch.cat((h_, t[:, :r0]), dim=1) for h_, t in zip(halos, (k1, v1, k2, v2))]
+                bnd = bwd(q[:, :r0], ext[0], ext[2], ext[1], ext[3], out[:, :r0], lse_b, dout[:, :r0], w1, w2, **kw)
+            if world > 1:
+                send = [bnd[1][:, :h1].contiguous(), bnd[3][:, :h1].contiguous(),
+                        bnd[2][:, :h2].contiguous(), bnd[4][:, :h2].contiguous()] if rank > 0 else None
+                ex = _Exchange(send, rank - 1, recv, rank + 1, group, "backward")
         if r0 < n:
             # interior rows: written straight into the rows [r0 - halo, n) of the local gradients
             a1, a2 = (r0 - h1, r0 - h2) if rank > 0 else (0, 0)
             bwd(q[:, r0:], k1[:, a1:], k2[:, a2:], v1[:, a1:], v2[:, a2:], out[:, r0:], lse_i, dout[:, r0:], w1, w2,
                 grads=(dq[:, r0:], dk1[:, a1:], dk2[:, a2:], dv1[:, a1:], dv2[:, a2:]), **kw)
+        with side:
+            if ex is not None:
+                ex.wait(timeout, blocking)
+        side.join(*ext, *(bnd or []), *(send or []))
         if rank > 0:
             # local rows [0, r0) of the first launch: rows below the interior's range are its alone, the
             # overlap [r0 - halo, r0) has a contribution from both launches
@@ -197,11 +252,9 @@ class SequenceParallelAttention(Function):
                 g_[:, :lo] = loc[:, :lo]
                 if lo < r0:
                     g_[:, lo:r0] += loc[:, lo:r0]
-        if ex is not None:
-            ex.wait(timeout, blocking)
-            if rank < world - 1:
-                for g_, r_, h_ in zip((dk1, dv1, dk2, dv2), ex.recv, (h1, h1, h2, h2)):
-                    g_[:, n - h_:] += r_
+        if ex is not None and rank < world - 1:
+            for g_, r_, h_ in zip((dk1, dv1, dk2, dv2), ex.recv, (h1, h1, h2, h2)):
+                g_[:, n - h_:] += r_
         return (dq, dk1, dk2, dv1, dv2) + (None,) * 7
 
 

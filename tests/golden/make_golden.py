@@ -20,6 +20,14 @@ Two families of fixtures are written:
     design is rebuilt here on ``torch.nn.functional.scaled_dot_product_attention``
     (CPU, fp64), which shares no code with the oracle.
 
+``stack_*.npz``  the reference's own decoder stack, ``TwoSimplicialTransformer``
+    with its ``Attention`` and ``FeedForward`` layers
+    (simplicial_attention/two_simplicial_transformer.py:25-141), run on CPU: the
+    sliding-window layers' ``attend`` (a Triton kernel) is swapped for the
+    reference's naive attend with windows that cover the sequence, where the two
+    are the same function.  Stored: the input activations, every parameter
+    (``param.<name>``) and the output.
+
 Each file stores the inputs as well as the outputs so that the tests do not
 depend on the random generator of the installed torch.
 """
@@ -87,6 +95,39 @@ def outer_case(name, b, n, hq, hk, d, w1, w2, seed):
     print("wrote", name)
 
 
+def stack_case(name, b, n, dim, depth, heads, kv_heads, dim_head, every, seed):
+    naive = _import_reference()
+    from simplicial_attention.two_simplicial_transformer import TwoSimplicialTransformer
+    torch.manual_seed(seed)
+    net = TwoSimplicialTransformer(dim, depth=depth, heads=heads, key_value_heads=kv_heads, dim_head=dim_head,
+                                   two_simplicial_attn_every=every,
+                                   two_simplicial_attn_kwargs=dict(w1=n, w2=n, qk_rmsnorm=True))
+
+    def attend(q, keys, values, **_):          # (b, n, h, d) in and out, as the sliding-window module calls it
+        hf = [t.permute(0, 2, 1, 3) for t in (q, *keys, *values)]
+        return naive(hf[0], (hf[1], hf[2]), (hf[3], hf[4]), causal=True).permute(0, 2, 1, 3)
+
+    swapped = 0
+    for attn, _ in net.layers:
+        if type(attn).__name__ == "SlidingWindowTwoSimplicialMHA":
+            attn.attend = attend
+            swapped += 1
+    assert swapped == depth // every
+    # norm gains away from one, so that a wrong gain-to-channel mapping cannot hide
+    with torch.no_grad():
+        for k, p_ in net.named_parameters():
+            if k.endswith("norm.weight") or "norms." in k or k.endswith("prenorm.weight"):
+                p_.mul_(1 + 0.2 * torch.randn_like(p_))
+    x = torch.randn(b, n, dim)
+    with torch.no_grad():
+        y = net(x)
+    arrays = {"x": x.numpy(), "y": y.numpy()}
+    arrays.update({"param." + k: v.detach().numpy() for k, v in net.state_dict().items()})
+    np.savez_compressed(os.path.join(HERE, f"stack_{name}.npz"), n=n, dim=dim, depth=depth, heads=heads, kv_heads=kv_heads,
+                        dim_head=dim_head, every=every, seed=seed, **arrays)
+    print("wrote", name, y.shape, len(arrays) - 2, "parameters")
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     # the reference's CPU-runnable configuration: b1 h2 n128 d32, full causal, fp32
@@ -96,3 +137,5 @@ if __name__ == "__main__":
     # windowed, same window ratio as the reference's GPU test (w1 = 2*w2)
     outer_case("b1h2n48d32_w16_8", 1, 48, 2, 2, 32, 16, 8, seed=5)
     outer_case("gqa_b1h4k2n40d64_w24_5", 1, 40, 4, 2, 64, 24, 5, seed=6)
+    # the reference decoder stack: 2 layers (standard, then sliding-window 2-simplicial), grouped-query heads
+    stack_case("b2n24dim32_depth2", 2, 24, 32, 2, 2, 1, 32, 2, seed=11)

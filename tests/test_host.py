@@ -49,3 +49,12 @@ def test_plugin_slot_receives_split_heads():
     out = m(torch.randn(2, 10, 64))
     assert out.shape == (2, 10, 64)
     assert seen["q"] == (2, 10, 4, 32) and seen["k"] == [(2, 10, 2, 32)] * 2 and seen["v"] == 2 and seen["causal"]
+
+
+def test_distinct_value_head_dim_is_rejected_at_construction():
+    """The kernels aggregate values over the key head dim; the module says so up front instead of failing at
+    the first forward (the reference accepts dim_head_values, simplicial_mha.py:34, and then fails in its kernels)."""
+    import pytest
+    with pytest.raises(ValueError):
+        sa.SlidingWindowTwoSimplicialMHA(dim=64, heads=2, dim_head=32, dim_head_values=16)
+    sa.SlidingWindowTwoSimplicialMHA(dim=64, heads=2, dim_head=32, dim_head_values=32)      # equal is fine

@@ -197,3 +197,31 @@ def test_errors_raise():
         sa.sliding_two_simplicial_attn(q, (q, q), (q, q), causal=False)
     with pytest.raises(sa._lib.Sa2Error):          # fp32 tensors cannot take the bf16 tensor-core path
         sa.sa2_forward(q, q, q, q, q, 4, 2, kernel="tcgen05")
+
+
+def test_wide_projection_uses_the_module_norms():
+    """32 heads x 128 channels with 8 kv heads is an 8192-channel projection: beyond what the fused per-head
+    norm keeps in shared memory in its backward, so the module must run the five RMSNorm modules, as the
+    reference does - forward and backward, with the same result as the fused path on a narrower slice."""
+    torch.manual_seed(0)
+    m = sa.SlidingWindowTwoSimplicialMHA(dim=64, heads=32, key_value_heads=8, dim_head=128, w1=16, w2=4).cuda()
+    assert sum(m.split_dims) == 8192 > m.fused_head_norm_max_channels
+    x = torch.randn(1, 32, 64, device="cuda", requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = m(x)
+    y.float().sum().backward()
+    assert torch.isfinite(y.float()).all() and torch.isfinite(x.grad).all()
+    assert sa.device_status() == 0
+
+
+def test_second_key_value_bias():
+    """K2_BIAS / V2_BIAS of the reference kernels (triton_two_simplicial_attention.py:105-106,175-176):
+    a constant added to every element of the second keys / values."""
+    ins = O.make_inputs(1, 96, 2, 2, 32, seed=12)
+    q, k1, k2, v1, v2 = (t.cuda().requires_grad_() for t in ins[:5])
+    out = sa.sliding_two_simplicial_attn(q, (k1, k2), (v1, v2), w1=40, w2=6, k2_bias=0.25, v2_bias=-0.5)
+    out.backward(ins[5].cuda())
+    ref = O.two_simplicial_fwd_bwd(ins[0], ins[1], ins[2] + 0.25, ins[3], ins[4] - 0.5, ins[5], 40, 6)
+    assert rel_err(out, ref["out"]) <= 1e-4
+    for t, k in zip((q, k1, k2, v1, v2), ("dq", "dk1", "dk2", "dv1", "dv2")):
+        assert rel_err(t.grad, ref[k]) <= 1e-4, k

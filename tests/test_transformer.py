@@ -92,3 +92,32 @@ def test_sample_with_and_without_cache():
     torch.manual_seed(7)
     b = model.sample(prompt, 30, temperature=1e-6, filter_thres=0.99, use_cache=False)
     assert a.shape == (2, 20) and torch.equal(a, b)              # greedy: identical continuations
+
+
+@pytest.mark.gpu
+def test_stack_matches_the_reference_stack_with_shared_weights():
+    """The decoder stack against the reference's own ``TwoSimplicialTransformer`` (golden written by
+    tests/golden/make_golden.py: the reference's modules on CPU, its sliding-window layers' Triton attend
+    swapped for its naive attend with windows that cover the sequence).  Same parameters, same input; here
+    the sliding-window layers run the CUDA kernels (fp32) and the fused per-head norm."""
+    import os
+
+    import numpy as np
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "stack_b2n24dim32_depth2.npz"))
+    n = int(z["n"])
+    net = TwoSimplicialTransformer(int(z["dim"]), depth=int(z["depth"]), heads=int(z["heads"]), key_value_heads=int(z["kv_heads"]),
+                                   dim_head=int(z["dim_head"]), two_simplicial_attn_every=int(z["every"]),
+                                   two_simplicial_attn_kwargs=dict(w1=n, w2=n, qk_rmsnorm=True))
+    state = {k[len("param."):]: torch.from_numpy(z[k]) for k in z.files if k.startswith("param.")}
+    assert set(state) == set(net.state_dict()), set(state) ^ set(net.state_dict())
+    net.load_state_dict(state)
+    net = net.cuda()
+    x, want = torch.from_numpy(z["x"]).cuda(), torch.from_numpy(z["y"])
+    for fused in (True, False):         # one kernel for the five per-head norms, or the separate modules
+        for attn, _ in net.layers:
+            if hasattr(attn, "fused_head_norm"):
+                attn.fused_head_norm = fused
+        with torch.no_grad():
+            got = net(x).cpu()
+        err = (got - want).abs().max().item() / want.abs().max().item()
+        assert err <= 1e-4, (fused, err)

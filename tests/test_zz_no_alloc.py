@@ -26,9 +26,10 @@ FP32_REL = 1e-4     # the fp32 tolerance used by the other GPU tests
 GRADS = ("dq", "dk1", "dk2", "dv1", "dv2")
 
 
-def backward_static(q, k1, k2, v1, v2, out, lse, dout, w1, w2, grad_dtype=torch.float32):
+def backward_static(q, k1, k2, v1, v2, out, lse, dout, w1, w2, grad_dtype=torch.float32, grads=None):
     """Call sa2_bwd_static_scratch with caller-owned inputs and outputs and no workspace."""
-    grads = [torch.empty(t.shape, dtype=grad_dtype, device=q.device) for t in (q, k1, k2, v1, v2)]
+    if grads is None:
+        grads = [torch.empty(t.shape, dtype=grad_dtype, device=q.device) for t in (q, k1, k2, v1, v2)]
     dq, dk1, dk2, dv1, dv2 = grads
     args = _lib.BwdArgs(
         _shape(q, k1, k2, w1, w2, q.shape[-1] ** -0.5, "simt"),
@@ -46,27 +47,33 @@ def backward_static(q, k1, k2, v1, v2, out, lse, dout, w1, w2, grad_dtype=torch.
     return status, grads
 
 
-def _case(b, n, hq, hk, d, w1, w2, seed, dtype):
-    ins = [t.cuda() for t in O.make_inputs(b, n, hq, hk, d, seed=seed, dtype=dtype)]
+def _case(b, n, hq, hk, d, w1, w2, seed, dtype, oracle=False):
+    cpu = O.make_inputs(b, n, hq, hk, d, seed=seed, dtype=dtype)
+    ins = [t.cuda() for t in cpu]
     q, k1, k2, v1, v2, do = ins
     out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel="simt")
     expect = sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel="simt", grad_dtype=torch.float32)
+    # the caller owns the outputs too: they exist before the call, which must then take no device memory at all
+    got = [torch.empty(t.shape, dtype=torch.float32, device=q.device) for t in (q, k1, k2, v1, v2)]
     torch.cuda.synchronize()
     free_before = torch.cuda.mem_get_info()[0]
-    status, got = backward_static(q, k1, k2, v1, v2, out, lse, do, w1, w2)
+    status, got = backward_static(q, k1, k2, v1, v2, out, lse, do, w1, w2, grads=got)
     torch.cuda.synchronize()
     free_after = torch.cuda.mem_get_info()[0]
     assert status == 0, _lib.lib().sa2_strerror(status)
+    assert free_after == free_before, "the call changed the amount of free device memory"
     for name, g, e in zip(GRADS, got, expect):
         assert rel_err(g, e) <= FP32_REL, (name, rel_err(g, e))
-    # the five gradient tensors above are the only device memory taken during the call
-    grad_bytes = sum(t.numel() * t.element_size() for t in got)
-    assert free_before - free_after <= grad_bytes + (4 << 20)
+    if oracle:
+        # and against the CPU oracle itself (fp32 tensors: nothing but fp32 rounding in between)
+        ref = O.two_simplicial_fwd_bwd(*cpu, w1, w2)
+        for name, g in zip(GRADS, got):
+            assert rel_err(g, ref[name]) <= FP32_REL, (name, rel_err(g, ref[name]))
 
 
 def test_two_calls_in_a_row_match_the_regular_entry_point():
     # the larger problem first, so that the second call finds stale row sums beyond its own size
-    _case(2, 200, 4, 2, 64, 70, 9, seed=41, dtype=torch.float32)
+    _case(2, 200, 4, 2, 64, 70, 9, seed=41, dtype=torch.float32, oracle=True)
     _case(1, 96, 2, 2, 32, 40, 6, seed=42, dtype=torch.bfloat16)
 
 
