@@ -46,8 +46,12 @@ constexpr int BQ_THREADS = 512;
 // Register hand-over between warpgroups.  Four warps per scheduler partition start with 128 registers a
 // thread; a group can only grow by what another has released, or its setmaxnreg never returns, so the
 // four budgets must add up to 4 * 128.
-constexpr int BQ_REGS_LAUNCH = 128, BQ_REGS_ISSUE = 40, BQ_REGS_COMPUTE = 120, BQ_REGS_FOLD = 192, BQ_REGS_BUILD = 160;
-static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BQ_REGS_FOLD + BQ_REGS_BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
+constexpr int BQ_REGS_LAUNCH = 128, BQ_REGS_ISSUE = 40, BQ_REGS_COMPUTE = 120;
+// head dim 64: the builders hold q, dO and the next k2 / v2 rows (160), the fold group dQ, U, W (192);
+// head dim 128: the builders hold a whole q row and k2 row (144), the fold group dQ and a whole dO row and v2 row (208)
+template <int D> struct BqRegs { static constexpr int FOLD = D == 64 ? 192 : 208, BUILD = D == 64 ? 160 : 144; };
+static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BqRegs<64>::FOLD + BqRegs<64>::BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
+static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BqRegs<128>::FOLD + BqRegs<128>::BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
 template <int D> struct BqCfg {
     static constexpr int CH = D / 64;                            // channel halves = CTAs per (query tile, split)
     static constexpr int KSTEPS = D / 16;                        // K = 16 steps of S and dP
@@ -424,7 +428,7 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
 __device__ __forceinline__ void bq_fold_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // Head dim 128: the fold thread of query row r forms row r of B_e = dO_i * v2_{i-e} for sweep e (the builder
-// group forms A_e), 64 channels at a time; the first 64 are fetched before the wait for the stage.
+// group forms A_e); the whole row is fetched before the wait for the stage.
 template <int D>
 __device__ __forceinline__ bool bq_build_b(const BqParams &P, const BqGeom &g, int e, int r, uint8_t *sB, uint64_t *bars,
                                            volatile int *abort_flag) {
@@ -435,22 +439,19 @@ __device__ __forceinline__ bool bq_build_b(const BqParams &P, const BqGeom &g, i
     const bool ok = i < kp.n && kk >= 0;
     const __nv_bfloat16 *dp = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, ok ? i : 0, h);
     const __nv_bfloat16 *vp = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p) + elem_off(kp.v2, b, ok ? kk : 0, hk);
+    uint4 dv[16], vv[16];
 #pragma unroll
-    for (int cb = 0; cb < 2; ++cb) {
-        uint4 dv[8], vv[8];
+    for (int cc = 0; cc < 16; ++cc) {
+        dv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(dp + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+        vv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(vp + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag, 3)) return false;
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-            dv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(dp + cb * 64 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
-            vv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(vp + cb * 64 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
-        }
-        if (cb == 0 && e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag, 3)) return false;
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-            uint4 bb;
-            bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
-            bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
-            *reinterpret_cast<uint4 *>(sB + cb * BqCfg<D>::BLK + sw128_offset(r, cc)) = bb;
-        }
+    for (int cc = 0; cc < 16; ++cc) {
+        uint4 bb;
+        bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
+        bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
+        *reinterpret_cast<uint4 *>(sB + (cc >> 3) * BqCfg<D>::BLK + sw128_offset(r, cc & 7)) = bb;
     }
     fence_proxy_async_smem();
     mbar_arrive(&bars[BQ_AB_FULL]);
@@ -655,10 +656,10 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
         reg_dealloc<BQ_REGS_COMPUTE>();
         err = bq_compute<D>(P, g, tmem, bars, abort_flag);
     } else if (warp < 12) {
-        reg_alloc<BQ_REGS_FOLD>();
+        reg_alloc<BqRegs<D>::FOLD>();
         err = bq_fold<D>(P, g, tmem, acc_k, acc_v, sB, bars, abort_flag);
     } else {
-        reg_alloc<BQ_REGS_BUILD>();
+        reg_alloc<BqRegs<D>::BUILD>();
         if (g.total > 0) err = bq_builder<D>(P, g, sA, sB, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
