@@ -30,12 +30,17 @@
 // Row i-e of the shared accumulators is touched by exactly one thread per
 // sweep, so the read-modify-write needs no atomics.
 //
-// Warps (512 threads, four aligned warpgroups): 0 TMA producer, then issuer of U / W; 1 TMEM owner and
-// issuer of S; 2 issuer of dP; 3 idle (head dim 128: TMA producer of the ring); 4-7 compute (P, G); 8-11 fold
-// (U, W into dQ / dK2 / dV2, concurrently with the next sweep's compute; head dim 128: also forms B_e);
-// 12-15 builders.  Every thread starts with 128 registers; the issuer
-// warpgroup releases all but 24 (setmaxnreg) and the fold and builder groups take them over.  TMEM columns: half h -> S/P [128h, 128h+64), dP/G [128h+64,
-// 128h+128); sweep parity p -> U [256+128p, +64), W [320+128p, +64).
+// Warps (512 threads, four aligned warpgroups): 0 issuer of U / W (head dim 64: after loading the tiles); 1 TMEM
+// owner and issuer of S; 2 issuer of dP; 3 idle (head dim 128: TMA producer of the ring); 4-7 compute (P, G).
+// Head dim 64: 8-11 a second compute group (the two take alternate units); 12-15 form A_e and B_e of the next
+// sweep, then fold U, W of the last one into dQ / dK2 / dV2 (q and dO rows stay in their registers for both).
+// Head dim 128: 8-11 form A_e; 12-15 form B_e and fold.
+// Every thread starts with 128 registers; the issuer warpgroup keeps 40 (setmaxnreg) and the others share the rest.
+// TMEM columns: S / dP buffer x -> S/P [128x, 128x+64), dP/G [128x+64, 128x+128); P and G overwrite S and dP,
+// so a buffer is busy from the issue of S / dP until the U / W products of its unit are done.  Head dim 64
+// has three such buffers in flight (issue, compute and U / W of different units overlap) and one U / W
+// accumulator pair [384, 512), which the fold group reads into registers before the next sweep's first
+// product; head dim 128 has two buffers (its ring has two slots) and U / W per sweep parity at [256 + 128p, +128).
 #pragma once
 #include "sa2_tc_bwd_k1.cuh"
 
@@ -47,9 +52,10 @@ constexpr int BQ_THREADS = 512;
 // thread; a group can only grow by what another has released, or its setmaxnreg never returns, so the
 // four budgets must add up to 4 * 128.
 constexpr int BQ_REGS_LAUNCH = 128, BQ_REGS_ISSUE = 40, BQ_REGS_COMPUTE = 120;
-// head dim 64: the builders hold q, dO and the next k2 / v2 rows (160), the fold group dQ, U, W (192);
+// head dim 64: warps 8-11 are a compute group; the fold group holds dQ, the q and dO rows, and either the next
+// k2 / v2 rows or a k2 row and chunks of U and W (232);
 // head dim 128: the builders hold a whole q row and k2 row (144), the fold group dQ and a whole dO row and v2 row (208)
-template <int D> struct BqRegs { static constexpr int FOLD = D == 64 ? 192 : 208, BUILD = D == 64 ? 160 : 144; };
+template <int D> struct BqRegs { static constexpr int FOLD = D == 64 ? 232 : 208, BUILD = D == 64 ? BQ_REGS_COMPUTE : 144; };
 static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BqRegs<64>::FOLD + BqRegs<64>::BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
 static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BqRegs<128>::FOLD + BqRegs<128>::BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
 template <int D> struct BqCfg {
@@ -61,6 +67,10 @@ template <int D> struct BqCfg {
     // ring of two 64-row units, each two [64 rows][64 channels] blocks of 8 KB
     static constexpr uint32_t KV_BYTES = D == 64 ? 3 * BLK : 2 * 16384;
     static constexpr uint32_t UBLK = 8192;                       // one channel block of a 64-row unit (head dim 128)
+    static constexpr int NBUF = D == 64 ? 3 : 2;                 // S / dP (P / G) buffers in TMEM
+    static constexpr int UWBUF = D == 64 ? 1 : 2;                // U / W accumulator pairs in TMEM
+    static constexpr int NCG = D == 64 ? 2 : 1;                  // compute groups
+    static constexpr uint32_t UW0 = NBUF * 128;                  // first TMEM column of U / W
 };
 constexpr int BQ_MAX_TILES = 3;          // K1/V1 tiles of one split (head dim 64)
 constexpr int BQ_ACC_STRIDE = 68;        // floats per accumulator row (64 + 4: conflict-free row-per-thread access)
@@ -70,13 +80,14 @@ enum BqBar {
     BQ_KV_FULL = 0,
     BQ_AB_FULL = 1,
     BQ_AB_EMPTY = 2,
-    BQ_S_FULL = 3,       // [2]
-    BQ_P_FULL = 5,       // [2]
-    BQ_W_FULL = 7,       // [2]
-    BQ_W_EMPTY = 9,      // [2]
-    BQ_G_DONE = 11,      // [2] per half: the U / W products of the unit have completed
-    BQ_KV_SLOT = 13,     // [2] head dim 128: the K1/V1 unit of the slot has landed
-    BQ_BAR_COUNT = 15
+    BQ_S_FULL = 3,       // [3] per buffer
+    BQ_P_FULL = 6,       // [3]
+    BQ_G_DONE = 9,       // [3] the U / W products of the buffer's unit have completed
+    BQ_W_FULL = 12,      // [2] per U / W accumulator pair
+    BQ_W_EMPTY = 14,     // [2] the fold group holds U / W of the sweep in registers
+    BQ_KV_SLOT = 16,     // [2] head dim 128: the K1/V1 unit of the slot has landed
+    BQ_FOLD_SYNC = 18,   // every fold thread has added its sweep into the shared accumulators
+    BQ_BAR_COUNT = 19
 };
 
 enum { ERR_BQ_PRODUCER = 256, ERR_BQ_MMA = 512, ERR_BQ_COMPUTE = 1024, ERR_BQ_BUILDER = 2048 };
@@ -141,99 +152,48 @@ __device__ __forceinline__ BqGeom bq_geom(const BqParams &P) {
     return g;
 }
 
-// ---------------------------------------------------------------- builders (warps 12-15)
-// One thread per query row forms row r of A_e and B_e for every sweep.  Head dim 64 keeps the
-// q / dO rows in registers; head dim 128 reads them (L2) with the k2 / v2 rows, one 64-channel block at
-// a time, so that the thread holds 128 registers of operands in both cases.
+// ---------------------------------------------------------------- head dim 128: builders of A_e (warps 8-11)
+// One thread per query row forms row r of A_e = q_i * k2_{i-e} for every sweep (the fold group forms B_e, see
+// bq_build_b); the whole row is fetched before the wait, so that the stage is rebuilt as soon as the tensor
+// cores release it.
 template <int D>
-__device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, uint8_t *sA, uint8_t *sB,
-                                          uint64_t *bars, volatile int *abort_flag) {
+__device__ __forceinline__ int bq_builder(const BqParams &P, const BqGeom &g, uint8_t *sA, uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
-    const int r = threadIdx.x - 384;
+    const int r = threadIdx.x - 256;
     const int h = blockIdx.y, b = blockIdx.z, hk = h / kp.g;
     const int i = g.i0 + r;
     const bool iv = i < kp.n;
     const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p);
-    const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p);
     const __nv_bfloat16 *qp = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, iv ? i : 0, h);
-    const __nv_bfloat16 *dp = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, iv ? i : 0, h);
-    const int nv = g.nsweeps;
-    if constexpr (D == 64) {
-        uint4 qv[8], dv[8];
+    for (int e = 0; e < g.nsweeps; ++e) {
+        const int kk = i + kp.off2 - e;
+        const bool ok = iv && kk >= 0;
+        const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+        uint4 qv[D / 8], kv[D / 8];
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) { qv[cc] = make_uint4(0, 0, 0, 0); dv[cc] = make_uint4(0, 0, 0, 0); }
-        if (iv) {
-#pragma unroll
-            for (int cc = 0; cc < 8; ++cc) {
-                qv[cc] = *reinterpret_cast<const uint4 *>(qp + cc * 8);
-                dv[cc] = *reinterpret_cast<const uint4 *>(dp + cc * 8);
-            }
+        for (int cc = 0; cc < D / 8; ++cc) {
+            qv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(qp + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            kv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kp2 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
         }
-        for (int v = 0; v < nv; ++v) {
-            const int e = v;
-            // fetch the second-key rows before waiting, so their latency overlaps the previous sweep
-            const int kk = i + kp.off2 - e;
-            const bool ok = iv && kk >= 0;
-            uint4 kv[8], vv[8];
-            if (ok) {
-                const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, kk, hk);
-                const __nv_bfloat16 *vp2 = v2 + elem_off(kp.v2, b, kk, hk);
+        if (e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag, 1)) return ERR_BQ_BUILDER;
 #pragma unroll
-                for (int cc = 0; cc < 8; ++cc) {
-                    kv[cc] = *reinterpret_cast<const uint4 *>(kp2 + cc * 8);
-                    vv[cc] = *reinterpret_cast<const uint4 *>(vp2 + cc * 8);
-                }
-            }
-            if (v >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (v - 1) & 1, abort_flag, 1)) return ERR_BQ_BUILDER;
-#pragma unroll
-            for (int cc = 0; cc < 8; ++cc) {
-                uint4 a = make_uint4(0, 0, 0, 0), bb = make_uint4(0, 0, 0, 0);
-                if (ok) {
-                    a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
-                    a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
-                    bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
-                    bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
-                }
-                *reinterpret_cast<uint4 *>(sA + sw128_offset(r, cc)) = a;
-                *reinterpret_cast<uint4 *>(sB + sw128_offset(r, cc)) = bb;
-            }
-            fence_proxy_async_smem();
-            mbar_arrive(&bars[BQ_AB_FULL]);
+        for (int cc = 0; cc < D / 8; ++cc) {
+            uint4 a;
+            a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
+            a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
+            *reinterpret_cast<uint4 *>(sA + (cc >> 3) * BqCfg<D>::BLK + sw128_offset(r, cc & 7)) = a;
         }
-    } else {
-        // head dim 128: this group forms A_e only (the fold group forms B_e, see bq_build_b); the whole row is
-        // fetched before the wait, so that the stage is rebuilt as soon as the tensor cores release it
-        for (int v = 0; v < nv; ++v) {
-            const int e = v;
-            const int kk = i + kp.off2 - e;
-            const bool ok = iv && kk >= 0;
-            const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
-            uint4 qv[16], kv[16];
-#pragma unroll
-            for (int cc = 0; cc < 16; ++cc) {
-                qv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(qp + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
-                kv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kp2 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
-            }
-            if (v >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (v - 1) & 1, abort_flag, 1)) return ERR_BQ_BUILDER;
-#pragma unroll
-            for (int cc = 0; cc < 16; ++cc) {
-                uint4 a;
-                a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
-                a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
-                *reinterpret_cast<uint4 *>(sA + (cc >> 3) * BqCfg<D>::BLK + sw128_offset(r, cc & 7)) = a;
-            }
-            fence_proxy_async_smem();
-            mbar_arrive(&bars[BQ_AB_FULL]);
-        }
+        fence_proxy_async_smem();
+        mbar_arrive(&bars[BQ_AB_FULL]);
     }
     return 0;
 }
 
 // ---------------------------------------------------------------- issuers of S (warp 1) and dP (warp 2), one lane each
-// Unit u (numbered over the whole kernel) is unit u % nunits of sweep u / nunits and uses TMEM half u & 1.
+// Unit u (numbered over the whole kernel) is unit u % nunits of sweep u / nunits and uses TMEM buffer u % NBUF.
 // One thread issues about one tcgen05.mma per 60-90 cycles, so the two product stages have an issuing
 // thread each; U / W are accumulated by one thread only, which keeps the summation order fixed.
-// which = 0: S = A_e K1^T into columns [128 half, +64); which = 1: dP = B_e V1^T into [128 half + 64, +64).
+// which = 0: S = A_e K1^T into columns [128 buf, +64); which = 1: dP = B_e V1^T into [128 buf + 64, +64).
 template <int D>
 __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t tmem, uint8_t *sKV, uint8_t *sAB,
                                             uint64_t *bars, volatile int *abort_flag) {
@@ -243,32 +203,32 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t
     if constexpr (D == 64) {
         if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_MMA;
     }
-    int u = 0;
+    int u = 0, buf = 0, use = 0;                         // use = u / NBUF: how often the buffer has been used before
     for (int e = 0; e < g.nsweeps; ++e) {
         if (!mbar_wait(&bars[BQ_AB_FULL], e & 1, abort_flag, 0, 1)) return ERR_BQ_MMA;
         for (int w = 0; w < g.nunits; ++w, ++u) {
-            const int half = u & 1;
             if constexpr (D == 64) {
-                // the buffer holds P / G of this half's previous unit until its U / W products are done
-                if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
+                // the buffer holds P / G of its previous unit until the U / W products of that unit are done
+                if (use >= 1 && !mbar_wait(&bars[BQ_G_DONE + buf], (use - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
             } else {
-                // the unit lands in slot `half` after the U / W products of the slot's previous unit are done
-                if (!mbar_wait(&bars[BQ_KV_SLOT + half], (u >> 1) & 1, abort_flag, 0, 3)) return ERR_BQ_MMA;
+                // the unit lands in slot `buf` after the U / W products of the slot's previous unit are done
+                if (!mbar_wait(&bars[BQ_KV_SLOT + buf], use & 1, abort_flag, 0, 3)) return ERR_BQ_MMA;
             }
             tc_fence_after();
-            const uint32_t d = tmem + half * 128 + which * 64;
+            const uint32_t d = tmem + buf * 128 + which * 64;
             if constexpr (D == 64) {
                 const uint64_t t = dT + (uint64_t)((w * 8192) >> 4);       // unit w: rows [64 w, +64) of the resident tiles
 #pragma unroll
                 for (int k = 0; k < 4; ++k) mma_ss(d, dA + 2 * k, t + 2 * k, IDESC_F, k > 0 ? 1u : 0u);
             } else {
-                const uint64_t t = dT + (uint64_t)((half * 2 * C::UBLK) >> 4);
+                const uint64_t t = dT + (uint64_t)((buf * 2 * C::UBLK) >> 4);
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                     mma_ss(d, dA + (uint64_t)(((k >> 2) * C::BLK) >> 4) + (uint64_t)((k & 3) * 2),
                            t + (uint64_t)(((k >> 2) * C::UBLK) >> 4) + (uint64_t)((k & 3) * 2), IDESC_F, k > 0 ? 1u : 0u);
             }
-            tc_commit(&bars[BQ_S_FULL + half]);
+            tc_commit(&bars[BQ_S_FULL + buf]);
+            if (++buf == C::NBUF) { buf = 0; ++use; }
         }
         tc_commit(&bars[BQ_AB_EMPTY]);
     }
@@ -302,58 +262,71 @@ __device__ __forceinline__ int bq_ring_producer(const BqParams &P, const BqGeom 
     return 0;
 }
 
-// ---------------------------------------------------------------- issuer of U, W (warp 0, one lane; head dim 64: also loads the tiles)
+// ---------------------------------------------------------------- issuers of U, W (one lane each)
+// part 0 (warp 0; head dim 64: after loading the tiles): U += G K1; part 1 (warp 3): W += P V1; part 2 (head dim
+// 128, warp 0): both.  Each accumulator has one issuing thread, which keeps its summation order fixed.
 template <int D>
-__device__ __forceinline__ int bq_mma_second(const BqParams &P, const BqGeom &g, const CUtensorMap *mapK, const CUtensorMap *mapV,
+__device__ __forceinline__ int bq_mma_second(const BqParams &P, const BqGeom &g, int part, const CUtensorMap *mapK, const CUtensorMap *mapV,
                                              uint32_t tmem, uint8_t *sK, uint8_t *sV, uint64_t *bars, volatile int *abort_flag) {
     using C = BqCfg<D>;
     constexpr uint32_t IDESC_G = idesc_bf16(128, 64, false, true);
     if constexpr (D == 64) {
-        const int hk = blockIdx.y / P.kp.g;
-        prefetch_tmap(mapK);
-        prefetch_tmap(mapV);
-        const int nt = g.nunits / 2;
-        mbar_arrive_expect_tx(&bars[BQ_KV_FULL], 2 * C::BLK * nt);
-        for (int t = 0; t < nt; ++t) {
-            const int row = g.ubase + TJ * t;
-            tma_load_4d(sK + (size_t)t * C::BLK, mapK, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
-            tma_load_4d(sV + (size_t)t * C::BLK, mapV, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+        if (part == 0) {
+            const int hk = blockIdx.y / P.kp.g;
+            prefetch_tmap(mapK);
+            prefetch_tmap(mapV);
+            const int nt = g.nunits / 2;
+            mbar_arrive_expect_tx(&bars[BQ_KV_FULL], 2 * C::BLK * nt);
+            for (int t = 0; t < nt; ++t) {
+                const int row = g.ubase + TJ * t;
+                tma_load_4d(sK + (size_t)t * C::BLK, mapK, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+                tma_load_4d(sV + (size_t)t * C::BLK, mapV, &bars[BQ_KV_FULL], 0, hk, row, blockIdx.z);
+            }
         }
         if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_PRODUCER;
     }
     // head dim 128: U / W take the CTA's 64-channel block of the unit as an MN-major B operand
     const uint64_t dK = smem_desc_sw128(smem_u32(sK) + (D == 64 ? 0 : g.chh * C::UBLK));
     const uint64_t dV = smem_desc_sw128(smem_u32(sV) + (D == 64 ? 0 : g.chh * C::UBLK));
-    int u = 0;
+    int u = 0, buf = 0, use = 0;
     for (int e = 0; e < g.nsweeps; ++e) {
-        const int wb = e & 1;
+        const int wb = e % C::UWBUF, wuse = e / C::UWBUF;
+        const uint32_t tu = tmem + C::UW0 + wb * 128, tw = tu + 64;
         for (int w = 0; w < g.nunits; ++w, ++u) {
-            const int half = u & 1;
-            if (!mbar_wait(&bars[BQ_P_FULL + half], (u >> 1) & 1, abort_flag, 0, 1)) return ERR_BQ_MMA;
-            if (w == 0 && e >= 2 && !mbar_wait(&bars[BQ_W_EMPTY + wb], ((e >> 1) - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
+            if (!mbar_wait(&bars[BQ_P_FULL + buf], use & 1, abort_flag, 0, 1)) return ERR_BQ_MMA;
+            // the fold group must have read the accumulators of the sweep that used them last
+            if (w == 0 && wuse >= 1 && !mbar_wait(&bars[BQ_W_EMPTY + wb], (wuse - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
             tc_fence_after();
-            const uint64_t off = (uint64_t)((D == 64 ? w * 8192 : half * 2 * C::UBLK) >> 4);
+            const uint64_t off = (uint64_t)((D == 64 ? w * 8192 : buf * 2 * C::UBLK) >> 4);
             const uint64_t kt = dK + off, vt = dV + off;
-            const uint32_t a = tmem + half * 128;
+            const uint32_t a = tmem + buf * 128;
             const uint32_t acc = w > 0 ? 1u : 0u;
-            mma_ts(tmem + 256 + wb * 128, a + 64, kt, IDESC_G, acc);           // U += G K1
-            mma_ts(tmem + 256 + wb * 128, a + 72, kt + 128, IDESC_G, 1u);
-            mma_ts(tmem + 256 + wb * 128, a + 80, kt + 256, IDESC_G, 1u);
-            mma_ts(tmem + 256 + wb * 128, a + 88, kt + 384, IDESC_G, 1u);
-            mma_ts(tmem + 320 + wb * 128, a, vt, IDESC_G, acc);                // W += P V1
-            mma_ts(tmem + 320 + wb * 128, a + 8, vt + 128, IDESC_G, 1u);
-            mma_ts(tmem + 320 + wb * 128, a + 16, vt + 256, IDESC_G, 1u);
-            mma_ts(tmem + 320 + wb * 128, a + 24, vt + 384, IDESC_G, 1u);
-            tc_commit(&bars[BQ_G_DONE + half]);
+            if (part != 1) {
+                mma_ts(tu, a + 64, kt, IDESC_G, acc);               // U += G K1
+                mma_ts(tu, a + 72, kt + 128, IDESC_G, 1u);
+                mma_ts(tu, a + 80, kt + 256, IDESC_G, 1u);
+                mma_ts(tu, a + 88, kt + 384, IDESC_G, 1u);
+            }
+            if (part != 0) {
+                mma_ts(tw, a, vt, IDESC_G, acc);                    // W += P V1
+                mma_ts(tw, a + 8, vt + 128, IDESC_G, 1u);
+                mma_ts(tw, a + 16, vt + 256, IDESC_G, 1u);
+                mma_ts(tw, a + 24, vt + 384, IDESC_G, 1u);
+            }
+            tc_commit(&bars[BQ_G_DONE + buf]);
+            if (++buf == C::NBUF) { buf = 0; ++use; }
         }
         tc_commit(&bars[BQ_W_FULL + wb]);
     }
     return 0;
 }
 
-// ---------------------------------------------------------------- compute (warps 4-7): P and G
+// ---------------------------------------------------------------- compute (warps 4-7; head dim 64: and 8-11): P and G
+// Head dim 64: group cg forms columns [32 cg, +32) of every unit, which halves the time between S / dP and P / G.
 template <int D>
-__device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, uint32_t tmem, uint64_t *bars, volatile int *abort_flag) {
+__device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, int cg, uint32_t tmem, uint64_t *bars, volatile int *abort_flag) {
+    using C = BqCfg<D>;
+    if (cg >= C::NCG) return 0;
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = (warp & 3) * 32 + lane;             // query row within the tile = TMEM lane
@@ -368,25 +341,37 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
         lse2 = kp.lse[o] * 1.4426950408889634f;
         dl = kp.delta[o];
     }
-    int u = 0;
+#ifdef SA2_PROF
+    long long seg_ld = 0, seg_math = 0, seg_st = 0;       // cycles in TMEM loads, arithmetic, TMEM stores and hand-over
+#endif
     {
-        for (int e = 0; e < g.nsweeps; ++e) {
+        int e = 0, w = 0;
+        for (int u = 0; u < g.total; ++u, ++w) {
+            if (w == g.nunits) { w = 0; ++e; }
             const bool sweep_ok = row_ok && (i + kp.off2 - e >= 0);
-            for (int w = 0; w < g.nunits; ++w, ++u) {
-                const int half = u & 1;
+            {
+                const int buf = u % C::NBUF, use = u / C::NBUF;
                 const int j0 = g.ubase + 64 * w;
                 const int d1 = i + kp.off1 - j0;
                 const int hi = sweep_ok ? min(d1, 63) : -1;         // valid columns: lo < col <= hi
                 const int lo = max(d1 - kp.w1, -j0 - 1);
-                if (!warp_wait(&bars[BQ_S_FULL + half], (u >> 1) & 1, abort_flag, 1)) return ERR_BQ_COMPUTE;
+                if (!warp_wait(&bars[BQ_S_FULL + buf], use & 1, abort_flag, 1)) return ERR_BQ_COMPUTE;
                 tc_fence_after();
                 const bool full = __all_sync(0xffffffffu, lo < 0 && hi >= 63);
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
+                const int ch_end = C::NCG == 2 ? cg + 1 : 2;
+#pragma unroll 1
+                for (int ch = C::NCG == 2 ? cg : 0; ch < ch_end; ++ch) {
                     uint32_t sv[32], dv[32], pp[16], gg[16];
-                    tmem_ld32(lane_addr + half * 128 + ch * 32, sv);
-                    tmem_ld32(lane_addr + half * 128 + 64 + ch * 32, dv);
+#ifdef SA2_PROF
+                    const long long seg_t0 = clock64();
+#endif
+                    tmem_ld32(lane_addr + buf * 128 + ch * 32, sv);
+                    tmem_ld32(lane_addr + buf * 128 + 64 + ch * 32, dv);
                     tmem_wait_ld();
+#ifdef SA2_PROF
+                    const long long seg_t1 = clock64();
+                    seg_ld += seg_t1 - seg_t0;
+#endif
                     if (full) {
 #pragma unroll
                         for (int x = 0; x < 32; x += 2) {
@@ -399,28 +384,39 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, ui
                         // valid columns are the integers in (lo, hi]: saturate(half + 1 - |col - mid|) is exactly 1
                         // inside and 0 outside (FMA pipe instead of compares and selects on the ALU pipe); the
                         // exponent is clamped so that a masked-out cell cannot give inf * 0
-                        const float mid = 0.5f * (float)(lo + 1 + hi), hwp = 0.5f * (float)(hi - lo - 1) + 1.f;
+                        const float mid = 0.5f * (float)(lo + 1 + hi) - (float)(ch * 32), hwp = 0.5f * (float)(hi - lo - 1) + 1.f;
 #pragma unroll
                         for (int x = 0; x < 32; x += 2) {
-                            const int col = ch * 32 + x;
-                            const float v0 = __saturatef(hwp - fabsf((float)col - mid));
-                            const float v1 = __saturatef(hwp - fabsf((float)(col + 1) - mid));
+                            const float v0 = __saturatef(hwp - fabsf((float)x - mid));
+                            const float v1 = __saturatef(hwp - fabsf((float)(x + 1) - mid));
                             const float p0 = ex2(fminf(fmaf(__uint_as_float(sv[x]), c, -lse2), 100.f)) * v0;
                             const float p1 = ex2(fminf(fmaf(__uint_as_float(sv[x + 1]), c, -lse2), 100.f)) * v1;
                             pp[x >> 1] = pack_bf16(p0, p1);
                             gg[x >> 1] = pack_bf16(p0 * (__uint_as_float(dv[x]) - dl), p1 * (__uint_as_float(dv[x + 1]) - dl));
                         }
                     }
+#ifdef SA2_PROF
+                    seg_math += clock64() - seg_t1;
+#endif
                     // P / G chunk over columns of S / dP that have already been read
-                    tmem_st16(lane_addr + half * 128 + ch * 16, pp);
-                    tmem_st16(lane_addr + half * 128 + 64 + ch * 16, gg);
+                    tmem_st16(lane_addr + buf * 128 + ch * 16, pp);
+                    tmem_st16(lane_addr + buf * 128 + 64 + ch * 16, gg);
                 }
+#ifdef SA2_PROF
+                const long long seg_t2 = clock64();
+#endif
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&bars[BQ_P_FULL + half]);
+                mbar_arrive(&bars[BQ_P_FULL + buf]);
+#ifdef SA2_PROF
+                seg_st += clock64() - seg_t2;
+#endif
             }
         }
     }
+    SA2_PROF_ADD(4, seg_ld);
+    SA2_PROF_ADD(5, seg_math);
+    SA2_PROF_ADD(6, seg_st);
     return 0;
 }
 
@@ -459,8 +455,9 @@ __device__ __forceinline__ bool bq_build_b(const BqParams &P, const BqGeom &g, i
 }
 
 template <int D>
-__device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v, uint8_t *sB,
+__device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v, uint8_t *sA, uint8_t *sB,
                                             uint64_t *bars, volatile int *abort_flag) {
+    using C = BqCfg<D>;
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = (warp & 3) * 32 + lane;             // query row within the tile = TMEM lane
@@ -475,90 +472,163 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
     const __nv_bfloat16 *qrow = reinterpret_cast<const __nv_bfloat16 *>(kp.q.p) + elem_off(kp.q, b, row_ok ? i : 0, h) + c0;
     const __nv_bfloat16 *dorow = reinterpret_cast<const __nv_bfloat16 *>(kp.dout.p) + elem_off(kp.dout, b, row_ok ? i : 0, h) + c0;
     const __nv_bfloat16 *k2 = reinterpret_cast<const __nv_bfloat16 *>(kp.k2.p) + c0;
+    const __nv_bfloat16 *v2 = reinterpret_cast<const __nv_bfloat16 *>(kp.v2.p) + c0;
+
+#ifdef SA2_PROF
+    long long seg_build = 0, seg_drain = 0;           // cycles after the waits of a build and of a fold
+#endif
+    // head dim 64: the q and dO rows serve every A_e / B_e and every fold of this thread
+    uint4 qv[8], dv[8];
+    if constexpr (D == 64) {
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+            qv[cc] = row_ok ? __ldg(reinterpret_cast<const uint4 *>(qrow + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            dv[cc] = row_ok ? __ldg(reinterpret_cast<const uint4 *>(dorow + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+
+    // row r of A_e and B_e for sweep e (head dim 64): the second-key rows are fetched before the wait for the stage
+    auto build = [&](int e) -> bool {
+        if constexpr (D == 64) {
+            const int kk = i + kp.off2 - e;
+            const bool ok = row_ok && kk >= 0;
+            const __nv_bfloat16 *kp2 = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+            const __nv_bfloat16 *vp2 = v2 + elem_off(kp.v2, b, ok ? kk : 0, hk);
+            uint4 kv[8], vv[8];
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                kv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kp2 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                vv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(vp2 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag, 3)) return false;
+#ifdef SA2_PROF
+            const long long seg_t0 = clock64();
+#endif
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                uint4 a = make_uint4(0u, 0u, 0u, 0u), bb = make_uint4(0u, 0u, 0u, 0u);
+                if (ok) {
+                    a.x = mul_bf16x2(qv[cc].x, kv[cc].x); a.y = mul_bf16x2(qv[cc].y, kv[cc].y);
+                    a.z = mul_bf16x2(qv[cc].z, kv[cc].z); a.w = mul_bf16x2(qv[cc].w, kv[cc].w);
+                    bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
+                    bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
+                }
+                *reinterpret_cast<uint4 *>(sA + sw128_offset(r, cc)) = a;
+                *reinterpret_cast<uint4 *>(sB + sw128_offset(r, cc)) = bb;
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&bars[BQ_AB_FULL]);
+#ifdef SA2_PROF
+            seg_build += clock64() - seg_t0;
+#endif
+            return true;
+        } else {
+            return bq_build_b<D>(P, g, e, r, sB, bars, abort_flag);
+        }
+    };
 
     auto drain = [&](int v) -> bool {
-        const int wb = v & 1, e = v;
-        if (!warp_wait(&bars[BQ_W_FULL + wb], (v >> 1) & 1, abort_flag, 1)) return false;
-        tc_fence_after();
+        const int wb = v % C::UWBUF, e = v;
         const int kk = i + kp.off2 - e;
         const bool ok = row_ok && kk >= 0;
+        // the k2 row is fetched before the wait, so that its latency overlaps the end of the sweep
+        uint4 k2r[8];
+        {
+            const __nv_bfloat16 *kr = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) k2r[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kr + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (!warp_wait(&bars[BQ_W_FULL + wb], (v / C::UWBUF) & 1, abort_flag, 1)) return false;
+        // A row of the shared accumulators is written by thread r in this sweep and by another thread in the
+        // last one: every fold thread must have finished that one first.
+        if (v >= 1 && !warp_wait(&bars[BQ_FOLD_SYNC], (v - 1) & 1, abort_flag, 2)) return false;
+        tc_fence_after();
+#ifdef SA2_PROF
+        const long long seg_t0 = clock64();
+#endif
         float *ak = acc_k + (size_t)(r + kp.w2 - 1 - e) * BQ_ACC_STRIDE;
         float *av = acc_v + (size_t)(r + kp.w2 - 1 - e) * BQ_ACC_STRIDE;
+        constexpr int CW = D == 64 ? 16 : 32;         // channels per step
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            uint32_t u[32], w[32];
-            tmem_ld32(lane_addr + 256 + wb * 128 + hf * 32, u);
-            tmem_ld32(lane_addr + 320 + wb * 128 + hf * 32, w);
+        for (int ch = 0; ch < 64 / CW; ++ch) {
+            uint4 qr[CW / 8], dr[CW / 8];
+#pragma unroll
+            for (int v8 = 0; v8 < CW / 8; ++v8) {
+                if constexpr (D == 64) {
+                    qr[v8] = qv[ch * (CW / 8) + v8];
+                    dr[v8] = dv[ch * (CW / 8) + v8];
+                } else {
+                    qr[v8] = __ldg(reinterpret_cast<const uint4 *>(qrow + ch * CW + v8 * 8));
+                    dr[v8] = __ldg(reinterpret_cast<const uint4 *>(dorow + ch * CW + v8 * 8));
+                }
+            }
+            uint32_t u[CW], w[CW];
+            if constexpr (CW == 16) {
+                tmem_ld16(lane_addr + C::UW0 + wb * 128 + ch * CW, u);
+                tmem_ld16(lane_addr + C::UW0 + wb * 128 + 64 + ch * CW, w);
+            } else {
+                tmem_ld32(lane_addr + C::UW0 + wb * 128 + ch * CW, u);
+                tmem_ld32(lane_addr + C::UW0 + wb * 128 + 64 + ch * CW, w);
+            }
             tmem_wait_ld();
+            if (ch == 64 / CW - 1) {
+                // U and W of the sweep are in registers: the tensor cores may overwrite them
+                tc_fence_before();
+                mbar_arrive(&bars[BQ_W_EMPTY + wb]);
+            }
             if (ok) {
-                // three passes (k2 -> dQ, q -> dK2, dO -> dV2); in each the four 16-byte loads are issued
-                // together, so a pass costs one memory latency instead of four
-                const __nv_bfloat16 *kr = k2 + elem_off(kp.k2, b, kk, hk) + hf * 32;
-                uint4 raw[4];
 #pragma unroll
-                for (int v8 = 0; v8 < 4; ++v8) raw[v8] = __ldg(reinterpret_cast<const uint4 *>(kr + v8 * 8));
-#pragma unroll
-                for (int v8 = 0; v8 < 4; ++v8) {
-                    const uint32_t kw[4] = {raw[v8].x, raw[v8].y, raw[v8].z, raw[v8].w};
+                for (int v8 = 0; v8 < CW / 8; ++v8) {
+                    const uint4 kraw = k2r[ch * (CW / 8) + v8];
+                    const uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
+                    const uint32_t qw[4] = {qr[v8].x, qr[v8].y, qr[v8].z, qr[v8].w};
+                    const uint32_t dw[4] = {dr[v8].x, dr[v8].y, dr[v8].z, dr[v8].w};
+                    float xk[8], xv[8];
 #pragma unroll
                     for (int z = 0; z < 4; ++z) {
                         const __nv_bfloat162 k2v = *reinterpret_cast<const __nv_bfloat162 *>(&kw[z]);
+                        const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162 *>(&qw[z]);
+                        const __nv_bfloat162 d2 = *reinterpret_cast<const __nv_bfloat162 *>(&dw[z]);
                         const int x = v8 * 8 + z * 2;
-                        dq[hf * 32 + x] = fmaf(__uint_as_float(u[x]), __low2float(k2v), dq[hf * 32 + x]);
-                        dq[hf * 32 + x + 1] = fmaf(__uint_as_float(u[x + 1]), __high2float(k2v), dq[hf * 32 + x + 1]);
+                        const float u0 = __uint_as_float(u[x]), u1 = __uint_as_float(u[x + 1]);
+                        dq[ch * CW + x] = fmaf(u0, __low2float(k2v), dq[ch * CW + x]);
+                        dq[ch * CW + x + 1] = fmaf(u1, __high2float(k2v), dq[ch * CW + x + 1]);
+                        xk[z * 2] = u0 * __low2float(q2);
+                        xk[z * 2 + 1] = u1 * __high2float(q2);
+                        xv[z * 2] = __uint_as_float(w[x]) * __low2float(d2);
+                        xv[z * 2 + 1] = __uint_as_float(w[x + 1]) * __high2float(d2);
                     }
-                }
 #pragma unroll
-                for (int pass = 0; pass < 2; ++pass) {
-                    const __nv_bfloat16 *mrow = (pass == 0 ? qrow : dorow) + hf * 32;
-                    float *arow = (pass == 0 ? ak : av) + hf * 32;
-#pragma unroll
-                    for (int v8 = 0; v8 < 4; ++v8) raw[v8] = __ldg(reinterpret_cast<const uint4 *>(mrow + v8 * 8));
-#pragma unroll
-                    for (int v8 = 0; v8 < 4; ++v8) {
-                        const uint32_t mw[4] = {raw[v8].x, raw[v8].y, raw[v8].z, raw[v8].w};
-                        float x8[8];
-#pragma unroll
-                        for (int z = 0; z < 4; ++z) {
-                            const __nv_bfloat162 m2 = *reinterpret_cast<const __nv_bfloat162 *>(&mw[z]);
-                            const int x = v8 * 8 + z * 2;
-                            const float t0 = __uint_as_float(pass == 0 ? u[x] : w[x]);
-                            const float t1 = __uint_as_float(pass == 0 ? u[x + 1] : w[x + 1]);
-                            x8[z * 2] = t0 * __low2float(m2);
-                            x8[z * 2 + 1] = t1 * __high2float(m2);
-                        }
-#pragma unroll
-                        for (int f4 = 0; f4 < 2; ++f4) {
-                            float4 *pa = reinterpret_cast<float4 *>(arow + v8 * 8 + f4 * 4);
-                            float4 tv = *pa;
-                            tv.x += x8[f4 * 4]; tv.y += x8[f4 * 4 + 1]; tv.z += x8[f4 * 4 + 2]; tv.w += x8[f4 * 4 + 3];
-                            *pa = tv;
-                        }
+                    for (int f4 = 0; f4 < 2; ++f4) {
+                        float4 *pk = reinterpret_cast<float4 *>(ak + ch * CW + v8 * 8 + f4 * 4);
+                        float4 *pv = reinterpret_cast<float4 *>(av + ch * CW + v8 * 8 + f4 * 4);
+                        float4 tk = *pk, tv = *pv;
+                        tk.x += xk[f4 * 4]; tk.y += xk[f4 * 4 + 1]; tk.z += xk[f4 * 4 + 2]; tk.w += xk[f4 * 4 + 3];
+                        tv.x += xv[f4 * 4]; tv.y += xv[f4 * 4 + 1]; tv.z += xv[f4 * 4 + 2]; tv.w += xv[f4 * 4 + 3];
+                        *pk = tk;
+                        *pv = tv;
                     }
                 }
             }
         }
-        tc_fence_before();
-        mbar_arrive(&bars[BQ_W_EMPTY + wb]);
+        mbar_arrive(&bars[BQ_FOLD_SYNC]);
+#ifdef SA2_PROF
+        seg_drain += clock64() - seg_t0;
+#endif
         return true;
     };
 
     const int nv = g.total > 0 ? g.nsweeps : 0;       // a split whose tiles all lie before the sequence start has no work
     int err = 0;
-    if constexpr (D == 128) {
-        if (nv > 0 && !bq_build_b<D>(P, g, 0, r, sB, bars, abort_flag)) err = ERR_BQ_COMPUTE;
-    }
+    if (nv > 0 && !build(0)) err = ERR_BQ_COMPUTE;
     for (int v = 0; v < nv && err == 0; ++v) {
-        if constexpr (D == 128) {
-            // B_e of the next sweep first: the tensor cores wait for it, U / W of this sweep have a buffer's slack
-            if (v + 1 < nv && !bq_build_b<D>(P, g, v + 1, r, sB, bars, abort_flag)) { err = ERR_BQ_COMPUTE; break; }
-        }
+        // the operands of the next sweep first: the tensor cores wait for them, U / W of this sweep arrive later
+        if (v + 1 < nv && !build(v + 1)) { err = ERR_BQ_COMPUTE; break; }
         if (!drain(v)) err = ERR_BQ_COMPUTE;
-        // A row of the shared accumulators is written by thread r in this sweep and by another thread in
-        // the next: every fold thread must have finished this one (all have arrived on W_EMPTY) first.
-        else if (!warp_wait(&bars[BQ_W_EMPTY + (v & 1)], (v >> 1) & 1, abort_flag, 2)) err = ERR_BQ_COMPUTE;
     }
 
+    SA2_PROF_ADD(4, seg_build);
+    SA2_PROF_ADD(5, seg_drain);
     // partial dQ of this split (NaN when a wait ran out, so that the failure is visible in the result)
     if (row_ok) {
         const bool bad = err != 0 || *abort_flag != 0;
@@ -572,16 +642,16 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 }
 
 template <int D>
-__device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v, uint8_t *sB,
+__device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v, uint8_t *sA, uint8_t *sB,
                                        uint64_t *bars, volatile int *abort_flag) {
     const KernelParams &kp = P.kp;
-    const int ft = threadIdx.x - 256;                 // 0..127 among the fold threads
+    const int ft = threadIdx.x - 384;                 // 0..127 among the fold threads
     const int h = blockIdx.y, b = blockIdx.z;
     const int acc_rows = 127 + kp.w2;
     // zero the shared accumulators (acc_v follows acc_k); only this group touches them
     for (int x = ft; x < 2 * acc_rows * BQ_ACC_STRIDE; x += 128) acc_k[x] = 0.f;
     bq_fold_sync();
-    const int err = bq_fold_body<D>(P, g, tmem, acc_k, acc_v, sB, bars, abort_flag);
+    const int err = bq_fold_body<D>(P, g, tmem, acc_k, acc_v, sA, sB, bars, abort_flag);
     // shared accumulators -> this CTA's 64 channels of its slab.  The barrier sits outside the body so
     // that a warp that gave up on a wait still reaches it.
     bq_fold_sync();
@@ -616,11 +686,14 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int x = 0; x < BQ_BAR_COUNT; ++x) {
-            const bool many = (x >= BQ_P_FULL && x < BQ_P_FULL + 2) || (x >= BQ_W_EMPTY && x < BQ_W_EMPTY + 2);
-            // S_FULL and AB_EMPTY collect one commit from each of the two first-product issuers
-            const bool two = (x >= BQ_S_FULL && x < BQ_S_FULL + 2) || x == BQ_AB_EMPTY;
-            // head dim 64: the builders form A_e and B_e; head dim 128: the builders A_e, the fold group B_e
-            mbar_init(&bars[x], x == BQ_AB_FULL ? (D == 128 ? 256u : 128u) : many ? 128u : two ? 2u : 1u);
+            const bool pfull = x >= BQ_P_FULL && x < BQ_P_FULL + 3;          // every compute thread
+            const bool many = (x >= BQ_W_EMPTY && x < BQ_W_EMPTY + 2) || x == BQ_FOLD_SYNC;
+            // S_FULL and AB_EMPTY collect one commit from each of the two first-product issuers; head dim 64:
+            // G_DONE and W_FULL one from each of the two second-product issuers
+            const bool two = (x >= BQ_S_FULL && x < BQ_S_FULL + 3) || x == BQ_AB_EMPTY ||
+                             (D == 64 && ((x >= BQ_G_DONE && x < BQ_G_DONE + 3) || (x >= BQ_W_FULL && x < BQ_W_FULL + 2)));
+            // head dim 64: the fold group forms A_e and B_e; head dim 128: the builders A_e, the fold group B_e
+            mbar_init(&bars[x], x == BQ_AB_FULL ? (D == 128 ? 256u : 128u) : pfull ? 128u * C::NCG : many ? 128u : two ? 2u : 1u);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -641,8 +714,9 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
 #endif
     if (warp < 4) {
         reg_dealloc<BQ_REGS_ISSUE>();                 // one instruction for the whole warpgroup
-        if (warp == 0) {
-            if (lane == 0 && g.total > 0) err = bq_mma_second<D>(P, g, &mapK, &mapV, tmem, sK, sV, bars, abort_flag);
+        if (warp == 0 || (D == 64 && warp == 3)) {
+            if (lane == 0 && g.total > 0)
+                err = bq_mma_second<D>(P, g, D == 64 ? (warp == 0 ? 0 : 1) : 2, &mapK, &mapV, tmem, sK, sV, bars, abort_flag);
             __syncwarp();
         } else if (warp == 1 || warp == 2) {
             if (lane == 0 && g.total > 0)
@@ -652,15 +726,21 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
             if (lane == 0 && g.total > 0) err = bq_ring_producer<D>(P, g, &mapK, &mapV, sK, sV, bars, abort_flag);
             __syncwarp();
         }
-    } else if (warp < 8) {
+    } else if (warp < 4 + 4 * C::NCG) {
+        // one call site for both compute groups: they run the same instructions, which the instruction caches
+        // of a scheduler then hold once
         reg_dealloc<BQ_REGS_COMPUTE>();
-        err = bq_compute<D>(P, g, tmem, bars, abort_flag);
+        err = bq_compute<D>(P, g, (warp >> 2) - 1, tmem, bars, abort_flag);
     } else if (warp < 12) {
-        reg_alloc<BqRegs<D>::FOLD>();
-        err = bq_fold<D>(P, g, tmem, acc_k, acc_v, sB, bars, abort_flag);
+        if constexpr (D == 64) {
+            reg_dealloc<BQ_REGS_COMPUTE>();
+        } else {
+            reg_alloc<BqRegs<D>::BUILD>();
+            if (g.total > 0) err = bq_builder<D>(P, g, sA, bars, abort_flag);
+        }
     } else {
-        reg_alloc<BqRegs<D>::BUILD>();
-        if (g.total > 0) err = bq_builder<D>(P, g, sA, sB, bars, abort_flag);
+        reg_alloc<BqRegs<D>::FOLD>();
+        err = bq_fold<D>(P, g, tmem, acc_k, acc_v, sA, sB, bars, abort_flag);
     }
     if (err) atomicOr(P.status, err);
     SA2_PROF_ADD(0, clock64() - prof_t0);
