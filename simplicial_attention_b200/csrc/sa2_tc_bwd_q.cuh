@@ -36,7 +36,8 @@
 // sweep, then fold U, W of the last one into dQ / dK2 / dV2 (q and dO rows stay in their registers for both).
 // Head dim 128: 8-11 form A_e; 12-15 form B_e and fold.
 // Every thread starts with 128 registers; the issuer warpgroup keeps 40 (setmaxnreg) and the others share the rest.
-// TMEM columns: S / dP buffer x -> S/P [128x, 128x+64), dP/G [128x+64, 128x+128); P and G overwrite S and dP,
+// TMEM columns: S / dP buffer x -> S/P [128x, 128x+64), dP/G [128x+64, 128x+128); P and G (bf16, 16 columns per
+// 32 keys) overwrite the first half of the S and dP columns of the same keys,
 // so a buffer is busy from the issue of S / dP until the U / W products of its unit are done.  Head dim 64
 // has three such buffers in flight (issue, compute and U / W of different units overlap) and one U / W
 // accumulator pair [384, 512), which the fold group reads into registers before the next sweep's first
@@ -302,16 +303,17 @@ __device__ __forceinline__ int bq_mma_second(const BqParams &P, const BqGeom &g,
             const uint32_t a = tmem + buf * 128;
             const uint32_t acc = w > 0 ? 1u : 0u;
             if (part != 1) {
+                // keys [32 x, +32) of G are 16 columns at 64 + 32 x, those of P at 32 x
                 mma_ts(tu, a + 64, kt, IDESC_G, acc);               // U += G K1
                 mma_ts(tu, a + 72, kt + 128, IDESC_G, 1u);
-                mma_ts(tu, a + 80, kt + 256, IDESC_G, 1u);
-                mma_ts(tu, a + 88, kt + 384, IDESC_G, 1u);
+                mma_ts(tu, a + 96, kt + 256, IDESC_G, 1u);
+                mma_ts(tu, a + 104, kt + 384, IDESC_G, 1u);
             }
             if (part != 0) {
                 mma_ts(tw, a, vt, IDESC_G, acc);                    // W += P V1
                 mma_ts(tw, a + 8, vt + 128, IDESC_G, 1u);
-                mma_ts(tw, a + 16, vt + 256, IDESC_G, 1u);
-                mma_ts(tw, a + 24, vt + 384, IDESC_G, 1u);
+                mma_ts(tw, a + 32, vt + 256, IDESC_G, 1u);
+                mma_ts(tw, a + 40, vt + 384, IDESC_G, 1u);
             }
             tc_commit(&bars[BQ_G_DONE + buf]);
             if (++buf == C::NBUF) { buf = 0; ++use; }
@@ -398,9 +400,10 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, in
 #ifdef SA2_PROF
                     seg_math += clock64() - seg_t1;
 #endif
-                    // P / G chunk over columns of S / dP that have already been read
-                    tmem_st16(lane_addr + buf * 128 + ch * 16, pp);
-                    tmem_st16(lane_addr + buf * 128 + 64 + ch * 16, gg);
+                    // P / G chunk over the first half of the columns of S / dP that this thread has just read (the
+                    // other columns of the buffer may still be unread by the other compute group)
+                    tmem_st16(lane_addr + buf * 128 + ch * 32, pp);
+                    tmem_st16(lane_addr + buf * 128 + 64 + ch * 32, gg);
                 }
 #ifdef SA2_PROF
                 const long long seg_t2 = clock64();
@@ -500,10 +503,7 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
                 kv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kp2 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
                 vv[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(vp2 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
             }
-            if (e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag, 3)) return false;
-#ifdef SA2_PROF
-            const long long seg_t0 = clock64();
-#endif
+            // the products too are formed before the wait: only the stores follow it
 #pragma unroll
             for (int cc = 0; cc < 8; ++cc) {
                 uint4 a = make_uint4(0u, 0u, 0u, 0u), bb = make_uint4(0u, 0u, 0u, 0u);
@@ -513,8 +513,17 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
                     bb.x = mul_bf16x2(dv[cc].x, vv[cc].x); bb.y = mul_bf16x2(dv[cc].y, vv[cc].y);
                     bb.z = mul_bf16x2(dv[cc].z, vv[cc].z); bb.w = mul_bf16x2(dv[cc].w, vv[cc].w);
                 }
-                *reinterpret_cast<uint4 *>(sA + sw128_offset(r, cc)) = a;
-                *reinterpret_cast<uint4 *>(sB + sw128_offset(r, cc)) = bb;
+                kv[cc] = a;
+                vv[cc] = bb;
+            }
+            if (e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag, 3)) return false;
+#ifdef SA2_PROF
+            const long long seg_t0 = clock64();
+#endif
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                *reinterpret_cast<uint4 *>(sA + sw128_offset(r, cc)) = kv[cc];
+                *reinterpret_cast<uint4 *>(sB + sw128_offset(r, cc)) = vv[cc];
             }
             fence_proxy_async_smem();
             mbar_arrive(&bars[BQ_AB_FULL]);
@@ -531,13 +540,12 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
         const int wb = v % C::UWBUF, e = v;
         const int kk = i + kp.off2 - e;
         const bool ok = row_ok && kk >= 0;
-        // the k2 row is fetched before the wait, so that its latency overlaps the end of the sweep
-        uint4 k2r[8];
-        {
-            const __nv_bfloat16 *kr = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+        // the first half of the k2 row is fetched before the wait, so that its latency overlaps the end of the
+        // sweep; the second half with the second half of U and W
+        const __nv_bfloat16 *kr = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+        uint4 k2r[4];
 #pragma unroll
-            for (int cc = 0; cc < 8; ++cc) k2r[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kr + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
-        }
+        for (int cc = 0; cc < 4; ++cc) k2r[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kr + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
         if (!warp_wait(&bars[BQ_W_FULL + wb], (v / C::UWBUF) & 1, abort_flag, 1)) return false;
         // A row of the shared accumulators is written by thread r in this sweep and by another thread in the
         // last one: every fold thread must have finished that one first.
@@ -548,7 +556,7 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 #endif
         float *ak = acc_k + (size_t)(r + kp.w2 - 1 - e) * BQ_ACC_STRIDE;
         float *av = acc_v + (size_t)(r + kp.w2 - 1 - e) * BQ_ACC_STRIDE;
-        constexpr int CW = D == 64 ? 16 : 32;         // channels per step
+        constexpr int CW = 32;                        // channels per step
 #pragma unroll
         for (int ch = 0; ch < 64 / CW; ++ch) {
             uint4 qr[CW / 8], dr[CW / 8];
@@ -563,12 +571,12 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
                 }
             }
             uint32_t u[CW], w[CW];
-            if constexpr (CW == 16) {
-                tmem_ld16(lane_addr + C::UW0 + wb * 128 + ch * CW, u);
-                tmem_ld16(lane_addr + C::UW0 + wb * 128 + 64 + ch * CW, w);
-            } else {
-                tmem_ld32(lane_addr + C::UW0 + wb * 128 + ch * CW, u);
-                tmem_ld32(lane_addr + C::UW0 + wb * 128 + 64 + ch * CW, w);
+            tmem_ld32(lane_addr + C::UW0 + wb * 128 + ch * CW, u);
+            tmem_ld32(lane_addr + C::UW0 + wb * 128 + 64 + ch * CW, w);
+            if (ch == 1) {
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc)
+                    k2r[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kr + 32 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
             }
             tmem_wait_ld();
             if (ch == 64 / CW - 1) {
@@ -579,7 +587,7 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
             if (ok) {
 #pragma unroll
                 for (int v8 = 0; v8 < CW / 8; ++v8) {
-                    const uint4 kraw = k2r[ch * (CW / 8) + v8];
+                    const uint4 kraw = k2r[v8];
                     const uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
                     const uint32_t qw[4] = {qr[v8].x, qr[v8].y, qr[v8].z, qr[v8].w};
                     const uint32_t dw[4] = {dr[v8].x, dr[v8].y, dr[v8].z, dr[v8].w};
