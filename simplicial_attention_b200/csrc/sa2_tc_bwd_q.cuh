@@ -14,8 +14,9 @@
 // half): S and dP contract over all 128 channels, U and W use the 64-channel block of K1 / V1 as their
 // B operand, so the fold, its registers and the shared accumulators are those of head dim 64.  The
 // accumulators and the two 32 KB operand tiles leave room for 64 KB of K1 / V1 only, so one CTA walks
-// the whole window (one split) and its 64-row units stream through a two-slot TMA ring, once per
-// sweep, from L2: slot h serves TMEM half h and is refilled when the U / W products of its unit are done.
+// the whole window (one split) and its 64-row units stream through a three-slot TMA ring, once per
+// sweep, from L2: a slot is refilled when the U / W products of its unit are done, one unit ahead of the
+// S / dP products that need it.
 //
 // Per offset e ("sweep") the builder warps form A_e = q_i * k2_{i-e} and
 // B_e = dO_i * v2_{i-e}; per 64-key half-tile the tensor cores compute
@@ -28,7 +29,7 @@
 //     dQ_i += U_e * k2_{i-e}                           (registers)
 //     dK2_{i-e} += U_e * q_i,  dV2_{i-e} += W_e * dO_i (fp32 rows in shared memory)
 // Row i-e of the shared accumulators is touched by exactly one thread per
-// sweep, so the read-modify-write needs no atomics.
+// sweep, so the read-modify-write needs no atomics (see BqAcc for how the rows are kept).
 //
 // Warps (512 threads, four aligned warpgroups): 0 issuer of U / W (head dim 64: after loading the tiles); 1 TMEM
 // owner and issuer of S; 2 issuer of dP; 3 idle (head dim 128: TMA producer of the ring); 4-7 compute (P, G).
@@ -65,8 +66,9 @@ template <int D> struct BqCfg {
     static constexpr uint32_t BLK = TJ * 128;                    // A_e / B_e: one [128 rows][64 channels] swizzled block
     static constexpr uint32_t TILE = (D / 64) * BLK;             // A_e or B_e
     // K1 / V1 in shared memory: head dim 64 keeps three 128-row tiles of 16 KB resident; head dim 128 has a
-    // ring of two 64-row units, each two [64 rows][64 channels] blocks of 8 KB
-    static constexpr uint32_t KV_BYTES = D == 64 ? 3 * BLK : 2 * 16384;
+    // ring of three 64-row units, each two [64 rows][64 channels] blocks of 8 KB
+    static constexpr int NSLOT = 3;
+    static constexpr uint32_t KV_BYTES = D == 64 ? 3 * BLK : NSLOT * 16384;
     static constexpr uint32_t UBLK = 8192;                       // one channel block of a 64-row unit (head dim 128)
     static constexpr int NBUF = D == 64 ? 3 : 2;                 // S / dP (P / G) buffers in TMEM
     static constexpr int UWBUF = D == 64 ? 1 : 2;                // U / W accumulator pairs in TMEM
@@ -74,8 +76,31 @@ template <int D> struct BqCfg {
     static constexpr uint32_t UW0 = NBUF * 128;                  // first TMEM column of U / W
 };
 constexpr int BQ_MAX_TILES = 3;          // K1/V1 tiles of one split (head dim 64)
-constexpr int BQ_ACC_STRIDE = 68;        // floats per accumulator row (64 + 4: conflict-free row-per-thread access)
-constexpr int BQ_MAX_W2 = 56;            // the shared accumulators hold 127 + w2 rows; beyond this they do not fit
+// Shared accumulators of dK2 / dV2: in sweep e thread r adds to slab row r + w2 - 1 - e, so 128 consecutive rows
+// are live at a time.
+// Head dim 64 keeps all 127 + w2 rows, 68 floats apart (64 + 4: the row-per-thread accesses of a warp spread over
+// all banks, and the offsets inside a row are compile-time constants).
+// Head dim 128 needs the space for its K1 / V1 ring and keeps a ring of 128 rows (slab row modulo 128): the top
+// row of a sweep is complete when thread 127 has added to it; one warp copies it to the slab in global memory at
+// the start of the next sweep, and thread 0 then writes (not adds to) the row that takes its place.  A row is 64
+// floats; its sixteen 16-byte chunks are XOR-ed with the row number instead of padding.
+constexpr int BQ_ACC_RING = 128;
+constexpr int BQ_ACC_STRIDE = 68;
+constexpr int BQ_MAX_W2 = 56;            // head dim 64: 127 + w2 accumulator rows must fit; also the tested range
+template <int D> struct BqAcc {
+    static constexpr bool RING = D == 128;
+    __host__ __device__ static int rows(int w2) { return RING ? BQ_ACC_RING : 127 + w2; }
+    __host__ __device__ static int row_floats() { return RING ? 64 : BQ_ACC_STRIDE; }
+    // float index of (slab row, channel col) inside one accumulator array, col % 4 == 0
+    __device__ static int off(int slab_row, int col) {
+        if constexpr (RING) {
+            const int pr = slab_row & (BQ_ACC_RING - 1);
+            return pr * 64 + ((((col >> 2) ^ pr) & 15) << 2);
+        } else {
+            return slab_row * BQ_ACC_STRIDE + col;
+        }
+    }
+};
 
 enum BqBar {
     BQ_KV_FULL = 0,
@@ -86,9 +111,10 @@ enum BqBar {
     BQ_G_DONE = 9,       // [3] the U / W products of the buffer's unit have completed
     BQ_W_FULL = 12,      // [2] per U / W accumulator pair
     BQ_W_EMPTY = 14,     // [2] the fold group holds U / W of the sweep in registers
-    BQ_KV_SLOT = 16,     // [2] head dim 128: the K1/V1 unit of the slot has landed
-    BQ_FOLD_SYNC = 18,   // every fold thread has added its sweep into the shared accumulators
-    BQ_BAR_COUNT = 19
+    BQ_KV_SLOT = 16,     // [3] head dim 128: the K1/V1 unit of the ring slot has landed
+    BQ_KV_FREE = 19,     // [3] head dim 128: the U / W products that read the slot have completed
+    BQ_FOLD_SYNC = 22,   // every fold thread has added its sweep into the shared accumulators
+    BQ_BAR_COUNT = 23
 };
 
 enum { ERR_BQ_PRODUCER = 256, ERR_BQ_MMA = 512, ERR_BQ_COMPUTE = 1024, ERR_BQ_BUILDER = 2048 };
@@ -108,7 +134,7 @@ struct BqParams {
 inline int bq_acc_rows(int w2) { return 127 + w2; }
 template <int D> inline size_t bq_smem_bytes(int w2) {
     return 1024 + (size_t)2 * BqCfg<D>::KV_BYTES + 2 * BqCfg<D>::TILE +
-           (size_t)2 * bq_acc_rows(w2) * BQ_ACC_STRIDE * sizeof(float) + 256;
+           (size_t)2 * BqAcc<D>::rows(w2) * BqAcc<D>::row_floats() * sizeof(float) + 256;
 }
 inline size_t bq_part_dq_bytes(const sa2_shape &s, int nsplit) { return (size_t)nsplit * s.b * s.n * s.hq * s.d * sizeof(float); }
 inline size_t bq_part_k2_bytes(const sa2_shape &s, int nsplit) {
@@ -205,15 +231,14 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t
         if (!mbar_wait(&bars[BQ_KV_FULL], 0, abort_flag)) return ERR_BQ_MMA;
     }
     int u = 0, buf = 0, use = 0;                         // use = u / NBUF: how often the buffer has been used before
+    int slot = 0, suse = 0;                              // head dim 128: ring slot u % NSLOT and u / NSLOT
     for (int e = 0; e < g.nsweeps; ++e) {
         if (!mbar_wait(&bars[BQ_AB_FULL], e & 1, abort_flag, 0, 1)) return ERR_BQ_MMA;
         for (int w = 0; w < g.nunits; ++w, ++u) {
-            if constexpr (D == 64) {
-                // the buffer holds P / G of its previous unit until the U / W products of that unit are done
-                if (use >= 1 && !mbar_wait(&bars[BQ_G_DONE + buf], (use - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
-            } else {
-                // the unit lands in slot `buf` after the U / W products of the slot's previous unit are done
-                if (!mbar_wait(&bars[BQ_KV_SLOT + buf], use & 1, abort_flag, 0, 3)) return ERR_BQ_MMA;
+            // the buffer holds P / G of its previous unit until the U / W products of that unit are done
+            if (use >= 1 && !mbar_wait(&bars[BQ_G_DONE + buf], (use - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
+            if constexpr (D == 128) {
+                if (!mbar_wait(&bars[BQ_KV_SLOT + slot], suse & 1, abort_flag, 0, 3)) return ERR_BQ_MMA;
             }
             tc_fence_after();
             const uint32_t d = tmem + buf * 128 + which * 64;
@@ -222,7 +247,7 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t
 #pragma unroll
                 for (int k = 0; k < 4; ++k) mma_ss(d, dA + 2 * k, t + 2 * k, IDESC_F, k > 0 ? 1u : 0u);
             } else {
-                const uint64_t t = dT + (uint64_t)((buf * 2 * C::UBLK) >> 4);
+                const uint64_t t = dT + (uint64_t)((slot * 2 * C::UBLK) >> 4);
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                     mma_ss(d, dA + (uint64_t)(((k >> 2) * C::BLK) >> 4) + (uint64_t)((k & 3) * 2),
@@ -230,6 +255,7 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t
             }
             tc_commit(&bars[BQ_S_FULL + buf]);
             if (++buf == C::NBUF) { buf = 0; ++use; }
+            if (++slot == C::NSLOT) { slot = 0; ++suse; }
         }
         tc_commit(&bars[BQ_AB_EMPTY]);
     }
@@ -244,22 +270,23 @@ __device__ __forceinline__ int bq_ring_producer(const BqParams &P, const BqGeom 
     const int hk = blockIdx.y / P.kp.g;
     prefetch_tmap(mapK);
     prefetch_tmap(mapV);
-    int w = 0;
+    int w = 0, slot = 0, suse = 0;
     for (int u = 0; u < g.total; ++u) {
-        const int half = u & 1;
-        if (u >= 2 && !mbar_wait(&bars[BQ_G_DONE + half], ((u >> 1) - 1) & 1, abort_flag, 32, 1)) return ERR_BQ_PRODUCER;
+        // the slot is free when the U / W products of the unit it held are done
+        if (suse >= 1 && !mbar_wait(&bars[BQ_KV_FREE + slot], (suse - 1) & 1, abort_flag, 32, 1)) return ERR_BQ_PRODUCER;
         const int row = g.ubase + 64 * w;
-        mbar_arrive_expect_tx(&bars[BQ_KV_SLOT + half], 4 * C::UBLK);
+        mbar_arrive_expect_tx(&bars[BQ_KV_SLOT + slot], 4 * C::UBLK);
 #pragma unroll
         for (int cb = 0; cb < 2; ++cb) {
-            tma_load_4d(sK + half * 2 * C::UBLK + cb * C::UBLK, mapK, &bars[BQ_KV_SLOT + half], cb * 64, hk, row, blockIdx.z);
-            tma_load_4d(sV + half * 2 * C::UBLK + cb * C::UBLK, mapV, &bars[BQ_KV_SLOT + half], cb * 64, hk, row, blockIdx.z);
+            tma_load_4d(sK + slot * 2 * C::UBLK + cb * C::UBLK, mapK, &bars[BQ_KV_SLOT + slot], cb * 64, hk, row, blockIdx.z);
+            tma_load_4d(sV + slot * 2 * C::UBLK + cb * C::UBLK, mapV, &bars[BQ_KV_SLOT + slot], cb * 64, hk, row, blockIdx.z);
         }
         if (++w == g.nunits) w = 0;
+        if (++slot == C::NSLOT) { slot = 0; ++suse; }
     }
     // every load must have landed before the CTA may exit, even if the consumers gave up
-    for (int u = max(0, g.total - 2); u < g.total; ++u)
-        if (!mbar_wait(&bars[BQ_KV_SLOT + (u & 1)], (u >> 1) & 1, abort_flag, 32)) return ERR_BQ_PRODUCER;
+    for (int u = max(0, g.total - C::NSLOT); u < g.total; ++u)
+        if (!mbar_wait(&bars[BQ_KV_SLOT + u % C::NSLOT], (u / C::NSLOT) & 1, abort_flag, 32)) return ERR_BQ_PRODUCER;
     return 0;
 }
 
@@ -289,7 +316,7 @@ __device__ __forceinline__ int bq_mma_second(const BqParams &P, const BqGeom &g,
     // head dim 128: U / W take the CTA's 64-channel block of the unit as an MN-major B operand
     const uint64_t dK = smem_desc_sw128(smem_u32(sK) + (D == 64 ? 0 : g.chh * C::UBLK));
     const uint64_t dV = smem_desc_sw128(smem_u32(sV) + (D == 64 ? 0 : g.chh * C::UBLK));
-    int u = 0, buf = 0, use = 0;
+    int u = 0, buf = 0, use = 0, slot = 0;
     for (int e = 0; e < g.nsweeps; ++e) {
         const int wb = e % C::UWBUF, wuse = e / C::UWBUF;
         const uint32_t tu = tmem + C::UW0 + wb * 128, tw = tu + 64;
@@ -298,7 +325,7 @@ __device__ __forceinline__ int bq_mma_second(const BqParams &P, const BqGeom &g,
             // the fold group must have read the accumulators of the sweep that used them last
             if (w == 0 && wuse >= 1 && !mbar_wait(&bars[BQ_W_EMPTY + wb], (wuse - 1) & 1, abort_flag, 0, 2)) return ERR_BQ_MMA;
             tc_fence_after();
-            const uint64_t off = (uint64_t)((D == 64 ? w * 8192 : buf * 2 * C::UBLK) >> 4);
+            const uint64_t off = (uint64_t)((D == 64 ? w * 8192 : slot * 2 * C::UBLK) >> 4);
             const uint64_t kt = dK + off, vt = dV + off;
             const uint32_t a = tmem + buf * 128;
             const uint32_t acc = w > 0 ? 1u : 0u;
@@ -316,7 +343,9 @@ __device__ __forceinline__ int bq_mma_second(const BqParams &P, const BqGeom &g,
                 mma_ts(tw, a + 40, vt + 384, IDESC_G, 1u);
             }
             tc_commit(&bars[BQ_G_DONE + buf]);
+            if constexpr (D == 128) tc_commit(&bars[BQ_KV_FREE + slot]);
             if (++buf == C::NBUF) { buf = 0; ++use; }
+            if (++slot == C::NSLOT) slot = 0;
         }
         tc_commit(&bars[BQ_W_FULL + wb]);
     }
@@ -458,8 +487,8 @@ __device__ __forceinline__ bool bq_build_b(const BqParams &P, const BqGeom &g, i
 }
 
 template <int D>
-__device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v, uint8_t *sA, uint8_t *sB,
-                                            uint64_t *bars, volatile int *abort_flag) {
+__device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, uint32_t tmem, float *acc_k, float *acc_v, float *slab,
+                                            uint8_t *sA, uint8_t *sB, uint64_t *bars, volatile int *abort_flag) {
     using C = BqCfg<D>;
     const KernelParams &kp = P.kp;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -554,8 +583,16 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 #ifdef SA2_PROF
         const long long seg_t0 = clock64();
 #endif
-        float *ak = acc_k + (size_t)(r + kp.w2 - 1 - e) * BQ_ACC_STRIDE;
-        float *av = acc_v + (size_t)(r + kp.w2 - 1 - e) * BQ_ACC_STRIDE;
+        const int arow = r + kp.w2 - 1 - e;           // slab row of this thread in this sweep
+        const bool fresh = BqAcc<D>::RING && (e == 0 || r == 0);      // ring: nothing has been added to the row yet
+        float *ak = acc_k + (size_t)arow * BQ_ACC_STRIDE, *av = acc_v + (size_t)arow * BQ_ACC_STRIDE;      // (padded layout)
+        if (BqAcc<D>::RING && v >= 1 && warp == 12) {
+            // the top row of the last sweep is complete: it goes to the slab before thread 0 reuses its place
+            const int trow = TQ - 1 + kp.w2 - e, arr = lane >> 4, c4 = (lane & 15) * 4;
+            const float4 t = *reinterpret_cast<const float4 *>((arr ? acc_v : acc_k) + BqAcc<D>::off(trow, c4));
+            *reinterpret_cast<float4 *>(slab + ((size_t)arr * (127 + kp.w2) + trow) * D + c4) = t;
+            __syncwarp();
+        }
         constexpr int CW = 32;                        // channels per step
 #pragma unroll
         for (int ch = 0; ch < 64 / CW; ++ch) {
@@ -584,7 +621,7 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
                 tc_fence_before();
                 mbar_arrive(&bars[BQ_W_EMPTY + wb]);
             }
-            if (ok) {
+            if (ok || BqAcc<D>::RING) {              // (a ring row is written even when this thread has nothing to add)
 #pragma unroll
                 for (int v8 = 0; v8 < CW / 8; ++v8) {
                     const uint4 kraw = k2r[v8];
@@ -601,20 +638,43 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
                         const float u0 = __uint_as_float(u[x]), u1 = __uint_as_float(u[x + 1]);
                         dq[ch * CW + x] = fmaf(u0, __low2float(k2v), dq[ch * CW + x]);
                         dq[ch * CW + x + 1] = fmaf(u1, __high2float(k2v), dq[ch * CW + x + 1]);
-                        xk[z * 2] = u0 * __low2float(q2);
-                        xk[z * 2 + 1] = u1 * __high2float(q2);
-                        xv[z * 2] = __uint_as_float(w[x]) * __low2float(d2);
-                        xv[z * 2 + 1] = __uint_as_float(w[x + 1]) * __high2float(d2);
+                        const bool add = ok || !BqAcc<D>::RING;      // (the padded layout skips rows with nothing to add)
+                        xk[z * 2] = add ? u0 * __low2float(q2) : 0.f;
+                        xk[z * 2 + 1] = add ? u1 * __high2float(q2) : 0.f;
+                        xv[z * 2] = add ? __uint_as_float(w[x]) * __low2float(d2) : 0.f;
+                        xv[z * 2 + 1] = add ? __uint_as_float(w[x + 1]) * __high2float(d2) : 0.f;
                     }
+                    if constexpr (BqAcc<D>::RING) {
+                        // both 16-byte pieces of both rows are read before any is written: the swizzled addresses
+                        // hide from the compiler that they are distinct, and it would order every read after the
+                        // last write
+                        float4 *pk[2], *pv[2], tk[2], tv[2];
 #pragma unroll
-                    for (int f4 = 0; f4 < 2; ++f4) {
-                        float4 *pk = reinterpret_cast<float4 *>(ak + ch * CW + v8 * 8 + f4 * 4);
-                        float4 *pv = reinterpret_cast<float4 *>(av + ch * CW + v8 * 8 + f4 * 4);
-                        float4 tk = *pk, tv = *pv;
-                        tk.x += xk[f4 * 4]; tk.y += xk[f4 * 4 + 1]; tk.z += xk[f4 * 4 + 2]; tk.w += xk[f4 * 4 + 3];
-                        tv.x += xv[f4 * 4]; tv.y += xv[f4 * 4 + 1]; tv.z += xv[f4 * 4 + 2]; tv.w += xv[f4 * 4 + 3];
-                        *pk = tk;
-                        *pv = tv;
+                        for (int f4 = 0; f4 < 2; ++f4) {
+                            const int off = BqAcc<D>::off(arow, ch * CW + v8 * 8 + f4 * 4);
+                            pk[f4] = reinterpret_cast<float4 *>(acc_k + off);
+                            pv[f4] = reinterpret_cast<float4 *>(acc_v + off);
+                            tk[f4] = tv[f4] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (!fresh) { tk[f4] = *pk[f4]; tv[f4] = *pv[f4]; }
+                        }
+#pragma unroll
+                        for (int f4 = 0; f4 < 2; ++f4) {
+                            tk[f4].x += xk[f4 * 4]; tk[f4].y += xk[f4 * 4 + 1]; tk[f4].z += xk[f4 * 4 + 2]; tk[f4].w += xk[f4 * 4 + 3];
+                            tv[f4].x += xv[f4 * 4]; tv[f4].y += xv[f4 * 4 + 1]; tv[f4].z += xv[f4 * 4 + 2]; tv[f4].w += xv[f4 * 4 + 3];
+                            *pk[f4] = tk[f4];
+                            *pv[f4] = tv[f4];
+                        }
+                    } else {
+#pragma unroll
+                        for (int f4 = 0; f4 < 2; ++f4) {
+                            float4 *pk = reinterpret_cast<float4 *>(ak + ch * CW + v8 * 8 + f4 * 4);
+                            float4 *pv = reinterpret_cast<float4 *>(av + ch * CW + v8 * 8 + f4 * 4);
+                            float4 tk = *pk, tv = *pv;
+                            tk.x += xk[f4 * 4]; tk.y += xk[f4 * 4 + 1]; tk.z += xk[f4 * 4 + 2]; tk.w += xk[f4 * 4 + 3];
+                            tv.x += xv[f4 * 4]; tv.y += xv[f4 * 4 + 1]; tv.z += xv[f4 * 4 + 2]; tv.w += xv[f4 * 4 + 3];
+                            *pk = tk;
+                            *pv = tv;
+                        }
                     }
                 }
             }
@@ -655,21 +715,31 @@ __device__ __forceinline__ int bq_fold(const BqParams &P, const BqGeom &g, uint3
     const KernelParams &kp = P.kp;
     const int ft = threadIdx.x - 384;                 // 0..127 among the fold threads
     const int h = blockIdx.y, b = blockIdx.z;
-    const int acc_rows = 127 + kp.w2;
-    // zero the shared accumulators (acc_v follows acc_k); only this group touches them
-    for (int x = ft; x < 2 * acc_rows * BQ_ACC_STRIDE; x += 128) acc_k[x] = 0.f;
+    const int slab_rows = 127 + kp.w2;
+    // this CTA's 64 channels of its slab (dK2 rows, then dV2 rows)
+    float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + g.qt) * P.nsplit + g.split) * (size_t)(2 * slab_rows * D) + g.chh * 64;
+    if constexpr (!BqAcc<D>::RING) {
+        // zero the accumulators (acc_v follows acc_k); only this group touches them
+        for (int x = ft; x < 2 * slab_rows * BQ_ACC_STRIDE; x += 128) acc_k[x] = 0.f;
+        bq_fold_sync();
+    }
+    const int err = bq_fold_body<D>(P, g, tmem, acc_k, acc_v, slab, sA, sB, bars, abort_flag);
+    // The barrier sits outside the body so that a warp that gave up on a wait still reaches it.
     bq_fold_sync();
-    const int err = bq_fold_body<D>(P, g, tmem, acc_k, acc_v, sA, sB, bars, abort_flag);
-    // shared accumulators -> this CTA's 64 channels of its slab.  The barrier sits outside the body so
-    // that a warp that gave up on a wait still reaches it.
-    bq_fold_sync();
-    float *slab = P.part_k2 + ((((size_t)b * kp.hq + h) * P.nqt + g.qt) * P.nsplit + g.split) * (size_t)(2 * acc_rows * D) + g.chh * 64;
+    // Ring: rows above the live ones went to the slab when they were completed; the live rows follow now, and
+    // the rows below them (second keys before the sequence start, when fewer than w2 sweeps ran) are zero.
+    const int nv = g.total > 0 ? g.nsweeps : 0;
+    const int live0 = BqAcc<D>::RING ? kp.w2 - nv : 0;                 // first slab row held in shared memory
+    const int rows = BqAcc<D>::RING && nv > 0 ? live0 + BQ_ACC_RING : slab_rows;
+    const bool held = !BqAcc<D>::RING || nv > 0;
     const bool bad = err != 0 || *abort_flag != 0;     // a CTA in which a wait ran out reports NaN
-    for (int x = ft; x < 2 * acc_rows * 16; x += 128) {
-        const int row = x >> 4, c4 = (x & 15) * 4;      // row over both arrays
-        float4 v = *reinterpret_cast<const float4 *>(acc_k + (size_t)row * BQ_ACC_STRIDE + c4);
+    for (int x = ft; x < 2 * rows * 16; x += 128) {
+        const int arr = x / (rows * 16), y = x - arr * rows * 16;
+        const int row = y >> 4, c4 = (y & 15) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (held && row >= live0) v = *reinterpret_cast<const float4 *>((arr ? acc_v : acc_k) + BqAcc<D>::off(row, c4));
         if (bad) v = make_float4(CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F);
-        *reinterpret_cast<float4 *>(slab + (size_t)row * D + c4) = v;
+        *reinterpret_cast<float4 *>(slab + ((size_t)arr * slab_rows + row) * D + c4) = v;
     }
     return err;
 }
@@ -685,9 +755,9 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     uint8_t *sA = sV + C::KV_BYTES;
     uint8_t *sB = sA + C::TILE;
     float *acc_k = reinterpret_cast<float *>(sB + C::TILE);
-    const int acc_rows = 127 + P.kp.w2;
-    float *acc_v = acc_k + (size_t)acc_rows * BQ_ACC_STRIDE;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(acc_v + (size_t)acc_rows * BQ_ACC_STRIDE);
+    const int acc_floats = BqAcc<D>::rows(P.kp.w2) * BqAcc<D>::row_floats();
+    float *acc_v = acc_k + acc_floats;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(acc_v + acc_floats);
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + BQ_BAR_COUNT);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
 

@@ -120,10 +120,13 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
     return *reinterpret_cast<uint32_t *>(&r);
 }
 
+#ifndef SA2_WARP_WAIT_SLEEP
+#define SA2_WARP_WAIT_SLEEP 64
+#endif
 // every lane of the warp waits; the result is uniform so that the .sync.aligned
 // tcgen05 instructions that follow are never reached by a partial warp
 __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int prof = -1) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, 64, prof));
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, SA2_WARP_WAIT_SLEEP, prof));
 }
 
 struct FwdGeom {
