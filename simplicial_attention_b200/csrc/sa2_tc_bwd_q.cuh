@@ -57,9 +57,6 @@ constexpr int BQ_REGS_LAUNCH = 128, BQ_REGS_ISSUE = 40, BQ_REGS_COMPUTE = 120;
 // head dim 64: warps 8-11 are a compute group; the fold group holds dQ, the q and dO rows, and either the next
 // k2 / v2 rows or a k2 row and chunks of U and W (232);
 // head dim 128: the builders hold a whole q row and k2 row (144), the fold group dQ and a whole dO row and v2 row (208)
-template <int D> struct BqRegs { static constexpr int FOLD = D == 64 ? 232 : 208, BUILD = D == 64 ? BQ_REGS_COMPUTE : 144; };
-static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BqRegs<64>::FOLD + BqRegs<64>::BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
-static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BqRegs<128>::FOLD + BqRegs<128>::BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
 template <int D> struct BqCfg {
     static constexpr int CH = D / 64;                            // channel halves = CTAs per (query tile, split)
     static constexpr int KSTEPS = D / 16;                        // K = 16 steps of S and dP
@@ -72,9 +69,15 @@ template <int D> struct BqCfg {
     static constexpr uint32_t UBLK = 8192;                       // one channel block of a 64-row unit (head dim 128)
     static constexpr int NBUF = D == 64 ? 3 : 2;                 // S / dP (P / G) buffers in TMEM
     static constexpr int UWBUF = D == 64 ? 1 : 2;                // U / W accumulator pairs in TMEM
-    static constexpr int NCG = D == 64 ? 2 : 1;                  // compute groups
+    static constexpr int NCG = 2;                                // compute groups (1 is still supported at head dim 128)
     static constexpr uint32_t UW0 = NBUF * 128;                  // first TMEM column of U / W
 };
+template <int D> struct BqRegs {
+    static constexpr bool BUILDERS = D == 128 && BqCfg<D>::NCG == 1;          // warps 8-11 form A_e instead of computing
+    static constexpr int FOLD = BUILDERS ? 208 : 232, BUILD = BUILDERS ? 144 : BQ_REGS_COMPUTE;
+};
+static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BqRegs<64>::FOLD + BqRegs<64>::BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
+static_assert(BQ_REGS_ISSUE + BQ_REGS_COMPUTE + BqRegs<128>::FOLD + BqRegs<128>::BUILD == 4 * BQ_REGS_LAUNCH, "register pool must balance");
 constexpr int BQ_MAX_TILES = 3;          // K1/V1 tiles of one split (head dim 64)
 // Shared accumulators of dK2 / dV2: in sweep e thread r adds to slab row r + w2 - 1 - e, so 128 consecutive rows
 // are live at a time.
@@ -560,6 +563,52 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
             seg_build += clock64() - seg_t0;
 #endif
             return true;
+        } else if constexpr (C::NCG == 2) {
+            // head dim 128 with two compute groups: this group forms A_e and B_e.  All four rows are fetched and
+            // multiplied before the wait (A_e, then B_e in two halves, to stay within the register budget).
+            const int kk = i + kp.off2 - e;
+            const bool ok = row_ok && kk >= 0;
+            const __nv_bfloat16 *qf = qrow - c0, *df = dorow - c0;
+            const __nv_bfloat16 *kp2 = k2 - c0 + elem_off(kp.k2, b, ok ? kk : 0, hk);
+            const __nv_bfloat16 *vp2 = v2 - c0 + elem_off(kp.v2, b, ok ? kk : 0, hk);
+            uint4 a[16], bb[16];
+            {
+                uint4 x[16];
+#pragma unroll
+                for (int cc = 0; cc < 16; ++cc) {
+                    a[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(qf + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                    x[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kp2 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int cc = 0; cc < 16; ++cc) {
+                    a[cc].x = mul_bf16x2(a[cc].x, x[cc].x); a[cc].y = mul_bf16x2(a[cc].y, x[cc].y);
+                    a[cc].z = mul_bf16x2(a[cc].z, x[cc].z); a[cc].w = mul_bf16x2(a[cc].w, x[cc].w);
+                }
+            }
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                uint4 x[8];
+#pragma unroll
+                for (int cc = 0; cc < 8; ++cc) {
+                    bb[hf * 8 + cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(df + (hf * 8 + cc) * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                    x[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(vp2 + (hf * 8 + cc) * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int cc = 0; cc < 8; ++cc) {
+                    uint4 &t = bb[hf * 8 + cc];
+                    t.x = mul_bf16x2(t.x, x[cc].x); t.y = mul_bf16x2(t.y, x[cc].y);
+                    t.z = mul_bf16x2(t.z, x[cc].z); t.w = mul_bf16x2(t.w, x[cc].w);
+                }
+            }
+            if (e >= 1 && !warp_wait(&bars[BQ_AB_EMPTY], (e - 1) & 1, abort_flag, 3)) return false;
+#pragma unroll
+            for (int cc = 0; cc < 16; ++cc) {
+                *reinterpret_cast<uint4 *>(sA + (cc >> 3) * C::BLK + sw128_offset(r, cc & 7)) = a[cc];
+                *reinterpret_cast<uint4 *>(sB + (cc >> 3) * C::BLK + sw128_offset(r, cc & 7)) = bb[cc];
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&bars[BQ_AB_FULL]);
+            return true;
         } else {
             return bq_build_b<D>(P, g, e, r, sB, bars, abort_flag);
         }
@@ -771,7 +820,7 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
             const bool two = (x >= BQ_S_FULL && x < BQ_S_FULL + 3) || x == BQ_AB_EMPTY ||
                              (D == 64 && ((x >= BQ_G_DONE && x < BQ_G_DONE + 3) || (x >= BQ_W_FULL && x < BQ_W_FULL + 2)));
             // head dim 64: the fold group forms A_e and B_e; head dim 128: the builders A_e, the fold group B_e
-            mbar_init(&bars[x], x == BQ_AB_FULL ? (D == 128 ? 256u : 128u) : pfull ? 128u * C::NCG : many ? 128u : two ? 2u : 1u);
+            mbar_init(&bars[x], x == BQ_AB_FULL ? (BqRegs<D>::BUILDERS ? 256u : 128u) : pfull ? 128u * C::NCG : many ? 128u : two ? 2u : 1u);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -810,11 +859,11 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
         reg_dealloc<BQ_REGS_COMPUTE>();
         err = bq_compute<D>(P, g, (warp >> 2) - 1, tmem, bars, abort_flag);
     } else if (warp < 12) {
-        if constexpr (D == 64) {
-            reg_dealloc<BQ_REGS_COMPUTE>();
-        } else {
+        if constexpr (BqRegs<D>::BUILDERS) {
             reg_alloc<BqRegs<D>::BUILD>();
             if (g.total > 0) err = bq_builder<D>(P, g, sA, bars, abort_flag);
+        } else {
+            reg_dealloc<BQ_REGS_COMPUTE>();
         }
     } else {
         reg_alloc<BqRegs<D>::FOLD>();
