@@ -40,20 +40,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Optional wait accounting (compile with -DSA2_PROF): lane 0 of every warp of one CTA adds the cycles
-// it spends in a wait to g_prof[8 * warp + slot]; sa2_prof_read() copies the table to the host.
+// Optional wait accounting (compile with -DSA2_PROF=<CTA>): lane 0 of every warp of one CTA adds the cycles
+// it spends in a wait to slot 8 * warp + slot of a table; sa2_prof_read() copies the table to the host.
 #ifdef SA2_PROF
 __device__ unsigned long long g_prof[512];
+// the cycles are summed in shared memory (a read-modify-write of global memory after every wait would itself
+// cost more than most waits) and copied out once, when the warp is done
+__device__ __forceinline__ unsigned long long *prof_slots() {
+    __shared__ unsigned long long s[8 * 24];          // up to 24 warps
+    return s;
+}
+__device__ __forceinline__ bool prof_lane() {
+    return blockIdx.x == SA2_PROF && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0;
+}
+__device__ __forceinline__ void prof_begin() {
+    if (prof_lane())
+        for (int k = 0; k < 8; ++k) prof_slots()[(threadIdx.x >> 5) * 8 + k] = 0;
+}
 __device__ __forceinline__ void prof_add(int slot, long long cycles) {
-    if (slot >= 0 && blockIdx.x == SA2_PROF && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0)
-        g_prof[(threadIdx.x >> 5) * 8 + slot] += (unsigned long long)cycles;
+    if (slot >= 0 && prof_lane()) prof_slots()[(threadIdx.x >> 5) * 8 + slot] += (unsigned long long)cycles;
+}
+__device__ __forceinline__ void prof_end() {
+    if (prof_lane())
+        for (int k = 0; k < 8; ++k) g_prof[(threadIdx.x >> 5) * 8 + k] += prof_slots()[(threadIdx.x >> 5) * 8 + k];
 }
 #define SA2_PROF_ADD(slot, cycles) sa2::sm100::prof_add(slot, cycles)
+#define SA2_PROF_END() sa2::sm100::prof_end()
 // segment timing: SA2_PROF_MARK(t) starts a segment, SA2_PROF_LAP(slot, t) books the time since and restarts
 #define SA2_PROF_MARK(t) long long t = clock64()
 #define SA2_PROF_LAP(slot, t) do { const long long _n = clock64(); sa2::sm100::prof_add(slot, _n - t); t = _n; } while (0)
 #else
 #define SA2_PROF_ADD(slot, cycles) do { } while (0)
+#define SA2_PROF_END() do { } while (0)
 #define SA2_PROF_MARK(t) do { } while (0)
 #define SA2_PROF_LAP(slot, t) do { } while (0)
 #endif

@@ -244,6 +244,7 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t
                 if (!mbar_wait(&bars[BQ_KV_SLOT + slot], suse & 1, abort_flag, 0, 3)) return ERR_BQ_MMA;
             }
             tc_fence_after();
+            SA2_PROF_MARK(seg);
             const uint32_t d = tmem + buf * 128 + which * 64;
             if constexpr (D == 64) {
                 const uint64_t t = dT + (uint64_t)((w * 8192) >> 4);       // unit w: rows [64 w, +64) of the resident tiles
@@ -256,7 +257,9 @@ __device__ __forceinline__ int bq_mma_first(const BqGeom &g, int which, uint32_t
                     mma_ss(d, dA + (uint64_t)(((k >> 2) * C::BLK) >> 4) + (uint64_t)((k & 3) * 2),
                            t + (uint64_t)(((k >> 2) * C::UBLK) >> 4) + (uint64_t)((k & 3) * 2), IDESC_F, k > 0 ? 1u : 0u);
             }
+            SA2_PROF_LAP(4, seg);                         // issue of the products
             tc_commit(&bars[BQ_S_FULL + buf]);
+            SA2_PROF_LAP(5, seg);                         // the commit
             if (++buf == C::NBUF) { buf = 0; ++use; }
             if (++slot == C::NSLOT) { slot = 0; ++suse; }
         }
@@ -838,6 +841,7 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     int err = 0;
 #ifdef SA2_PROF
     const long long prof_t0 = clock64();
+    sa2::sm100::prof_begin();
 #endif
     if (warp < 4) {
         reg_dealloc<BQ_REGS_ISSUE>();                 // one instruction for the whole warpgroup
@@ -871,6 +875,7 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
     }
     if (err) atomicOr(P.status, err);
     SA2_PROF_ADD(0, clock64() - prof_t0);
+    SA2_PROF_END();
 
     tc_fence_before();
     __syncthreads();

@@ -491,6 +491,7 @@ fwd128_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     int err = 0;
 #ifdef SA2_PROF
     const long long prof_t0 = clock64();
+    sa2::sm100::prof_begin();
 #endif
     if (warp < 4) {
         reg_dealloc<REGS_ISSUE>();                    // one instruction for the whole warpgroup
@@ -551,6 +552,7 @@ fwd128_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ 
     }
     if (err) atomicOr(P.status, err);
     SA2_PROF_ADD(0, clock64() - prof_t0);
+    SA2_PROF_END();
 
     tc_fence_before();
     __syncthreads();
