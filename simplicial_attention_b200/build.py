@@ -45,16 +45,17 @@ def is_stale() -> bool:
     return any(os.path.getmtime(f) > t for f in _inputs())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile libsa2.so if it is missing or older than its sources."""
-    if not force and not is_stale():
+def build(force: bool = False, verbose: bool = False, out: str = LIB, defines: tuple[str, ...] = ()) -> str:
+    """Compile libsa2.so if it is missing or older than its sources.  ``out`` and ``defines`` make a second
+    build beside it (the diagnostic build with wait accounting, see waitprof.py); such a build is always redone."""
+    if out == LIB and not force and not is_stale():
         return LIB
     cmd = [
         _nvcc(), "-shared", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo",
         *ARCH_FLAGS,
         "-I", os.path.join(ROOT, "include"), "-I", CSRC,
-        "--expt-relaxed-constexpr",
-        "-o", LIB, *sources(),
+        "--expt-relaxed-constexpr", *["-D" + d for d in defines],
+        "-o", out, *sources(),
     ]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
@@ -64,7 +65,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
     if verbose:
         print(res.stderr, file=sys.stderr)
-    return LIB
+    return out
 
 
 if __name__ == "__main__":
