@@ -514,6 +514,10 @@ def main():
     big = args.workload == "C5"
     if args.workload in ("C5s", "C3s"):
         args.no_extra = args.no_e2e = args.no_cpu_baseline = True
+    numa_cpus, all_cpus = None, (os.sched_getaffinity(0) if hasattr(os, "sched_getaffinity") else None)
+    if not (args.no_e2e or big):
+        from simplicial_attention_b200.host import bind_to_device_cpus
+        numa_cpus = bind_to_device_cpus(dev)        # before the pinned buffers are allocated
     host, devt = make_inputs(cfg, seed=1234 + rank, dtype=dtype, device=dev, pin=not (args.no_e2e or big))
     w1, w2 = cfg["w1"], cfg["w2"]
     fl = work_flops(cfg)
@@ -569,9 +573,12 @@ def main():
                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host),
                "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in outs_h),
                "ms_per_step": e2e_ms, "h2d_gbs_min_rank": gbs[0].item(), "d2h_gbs_min_rank": gbs[1].item(),
+               "host_cpus_rank0": (len(numa_cpus) if numa_cpus else "unchanged"),
                "note": "throughput of back-to-back pipelined calls (copies of step s+1 overlap the kernels of step s), "
                        "not the latency of one call; GB/s = bytes / time the copy stream was busy, slowest rank"}
         del pipe, outs_h
+    if numa_cpus and all_cpus:
+        os.sched_setaffinity(0, all_cpus)           # the CPU baseline below uses every core again
 
     # ---- extra records: the partitioned multi-GPU paths
     seq = c5 = None
