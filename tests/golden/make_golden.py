@@ -1,9 +1,9 @@
 """Generate the golden fixtures in this directory.
 
-Run in a container that has the reference checked out (default
-``/root/reference``; override with ``SA2_REFERENCE``):
+Run where the reference project is checked out; ``SA2_REFERENCE`` (or the first
+argument) names its directory:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <path to the reference checkout>
 
 Two families of fixtures are written:
 
@@ -39,10 +39,12 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("SA2_REFERENCE", "/root/reference")
+REF = (sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SA2_REFERENCE")) or ""
 
 
 def _import_reference():
+    if not os.path.isdir(os.path.join(REF, "simplicial_attention")):
+        sys.exit("make_golden.py: pass the directory of the reference checkout (argument or SA2_REFERENCE)")
     stub = types.ModuleType("opt_einsum")
     stub.contract = lambda eq, *ops: torch.einsum(eq, *ops)
     sys.modules["opt_einsum"] = stub
