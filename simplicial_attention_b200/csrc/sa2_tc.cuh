@@ -145,7 +145,7 @@ inline int bwd_q_launch(const KernelParams &kp, const sa2_shape &s, const CUtens
     }
     bwd_q_kernel<D><<<dim3(Q.nqt * Q.nsplit * BqCfg<D>::CH, kp.hq, kp.b), BQ_THREADS, smem, st>>>(ringK, ringV, Q);
     if (cudaGetLastError() != cudaSuccess) return SA2_ERR_CUDA;
-    const int64_t work = ((int64_t)kp.b * kp.n * kp.hq + (int64_t)kp.b * kp.nk2 * kp.hk) * (D / 4);
+    const int64_t work = ((Q.nsplit == 1 ? 0 : (int64_t)kp.b * kp.n * kp.hq) + (int64_t)kp.b * kp.nk2 * kp.hk) * (D / 4);
     bwd_q_reduce_kernel<D><<<(unsigned)((work + 255) / 256), 256, 0, st>>>(Q);
     return cudaGetLastError() == cudaSuccess ? SA2_OK : SA2_ERR_CUDA;
 }

@@ -139,7 +139,8 @@ template <int D> inline size_t bq_smem_bytes(int w2) {
     return 1024 + (size_t)2 * BqCfg<D>::KV_BYTES + 2 * BqCfg<D>::TILE +
            (size_t)2 * BqAcc<D>::rows(w2) * BqAcc<D>::row_floats() * sizeof(float) + 256;
 }
-inline size_t bq_part_dq_bytes(const sa2_shape &s, int nsplit) { return (size_t)nsplit * s.b * s.n * s.hq * s.d * sizeof(float); }
+// (a query tile with one split writes dQ itself and needs no partials)
+inline size_t bq_part_dq_bytes(const sa2_shape &s, int nsplit) { return nsplit == 1 ? 0 : (size_t)nsplit * s.b * s.n * s.hq * s.d * sizeof(float); }
 inline size_t bq_part_k2_bytes(const sa2_shape &s, int nsplit) {
     const size_t nqt = (s.n + TQ - 1) / TQ;
     return (size_t)s.b * s.hq * nqt * nsplit * 2 * bq_acc_rows(s.w2) * s.d * sizeof(float);
@@ -749,14 +750,27 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 
     SA2_PROF_ADD(4, seg_build);
     SA2_PROF_ADD(5, seg_drain);
-    // partial dQ of this split (NaN when a wait ran out, so that the failure is visible in the result)
+    // dQ of this row (NaN when a wait ran out, so that the failure is visible in the result): with one split per
+    // query tile it is final and goes straight to the gradient, otherwise a partial for the reduction kernel
     if (row_ok) {
         const bool bad = err != 0 || *abort_flag != 0;
-        float *dst = P.part_dq + ((((size_t)g.split * kp.b + b) * kp.n + i) * kp.hq + h) * D + c0;
+        if (P.nsplit == 1) {
+            const bool gbf16 = kp.grad_bf16 != 0;
+            const int64_t o = elem_off(kp.dq, b, i, h) + c0;
 #pragma unroll
-        for (int x = 0; x < 64; x += 4)
-            *reinterpret_cast<float4 *>(dst + x) = bad ? make_float4(CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F)
-                                                       : make_float4(dq[x], dq[x + 1], dq[x + 2], dq[x + 3]);
+            for (int x = 0; x < 64; x += 4) {
+                float v[4];
+#pragma unroll
+                for (int z = 0; z < 4; ++z) v[z] = bad ? CUDART_NAN_F : dq[x + z] * kp.scale;
+                store_vec<4>(kp.dq.p, o + x, gbf16, v);
+            }
+        } else {
+            float *dst = P.part_dq + ((((size_t)g.split * kp.b + b) * kp.n + i) * kp.hq + h) * D + c0;
+#pragma unroll
+            for (int x = 0; x < 64; x += 4)
+                *reinterpret_cast<float4 *>(dst + x) = bad ? make_float4(CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F, CUDART_NAN_F)
+                                                           : make_float4(dq[x], dq[x + 1], dq[x + 2], dq[x + 3]);
+        }
     }
     return err;
 }
@@ -887,7 +901,7 @@ bwd_q_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ C
 
 // ---------------------------------------------------------------------------
 // Reduction of the partials: one thread per 4 channels of an output row.
-//   dq[b,i,h]   = scale * sum_split part_dq[split][b][i][h]
+//   dq[b,i,h]   = scale * sum_split part_dq[split][b][i][h]        (two or more splits only)
 //   dk2[b,k,hk] = scale * sum_{h in group} sum_{tiles touching k} sum_split slab_k[...]
 //   dv2[b,k,hk] =         same over slab_v
 // Row k (position k - off2 in query coordinates) lies in the slab of query tile
@@ -899,7 +913,7 @@ __global__ void bwd_q_reduce_kernel(const BqParams P) {
     constexpr int TPR = D / 4;                          // threads per row
     const KernelParams &kp = P.kp;
     const int acc_rows = 127 + kp.w2;
-    const int64_t nq = (int64_t)kp.b * kp.n * kp.hq * TPR;
+    const int64_t nq = P.nsplit == 1 ? 0 : (int64_t)kp.b * kp.n * kp.hq * TPR;      // one split: dQ is already in place
     const int64_t nk = (int64_t)kp.b * kp.nk2 * kp.hk * TPR;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const bool gbf16 = kp.grad_bf16 != 0;
