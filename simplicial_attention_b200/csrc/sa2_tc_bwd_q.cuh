@@ -12,16 +12,15 @@
 // two splits.
 // Head dim 128: a CTA produces 64 of the 128 output channels (blockIdx.x also carries the channel
 // half): S and dP contract over all 128 channels, U and W use the 64-channel block of K1 / V1 as their
-// B operand, so the fold, its registers and the shared accumulators are those of head dim 64.  The
-// accumulators and the two 32 KB operand tiles leave room for 64 KB of K1 / V1 only, so one CTA walks
-// the whole window (one split) and its 64-row units stream through a three-slot TMA ring, once per
-// sweep, from L2: a slot is refilled when the U / W products of its unit are done, one unit ahead of the
-// S / dP products that need it.
+// B operand, so the fold, its registers and the shared accumulators are those of head dim 64.  Shared
+// memory cannot hold a window at this head dim, so one CTA walks the whole window (one split) and its
+// 64-row units stream through a three-slot TMA ring (32 KB per slot), once per sweep, from L2: a slot is
+// refilled when the U / W products of its unit are done, one unit ahead of the S / dP products that need it.
 //
-// Per offset e ("sweep") the builder warps form A_e = q_i * k2_{i-e} and
-// B_e = dO_i * v2_{i-e}; per 64-key half-tile the tensor cores compute
+// Per offset e ("sweep") one warp group forms A_e = q_i * k2_{i-e} and B_e = dO_i * v2_{i-e}; per 64-key
+// unit the tensor cores compute
 //     S = A_e K1^T      dP = B_e V1^T                 (rows i, columns j)
-// the compute warps (one thread per query row) form
+// the compute warps (one thread per query row and half of the unit's columns) form
 //     P = exp2(c S - lse2_i)     G = P * (dP - D_i)    (bf16, back into TMEM)
 // and the tensor cores accumulate over the sweep
 //     U_e += G K1       W_e += P V1                    (K1/V1 as MN-major B)
@@ -31,18 +30,19 @@
 // Row i-e of the shared accumulators is touched by exactly one thread per
 // sweep, so the read-modify-write needs no atomics (see BqAcc for how the rows are kept).
 //
-// Warps (512 threads, four aligned warpgroups): 0 issuer of U / W (head dim 64: after loading the tiles); 1 TMEM
-// owner and issuer of S; 2 issuer of dP; 3 idle (head dim 128: TMA producer of the ring); 4-7 compute (P, G).
-// Head dim 64: 8-11 a second compute group (the two take alternate units); 12-15 form A_e and B_e of the next
-// sweep, then fold U, W of the last one into dQ / dK2 / dV2 (q and dO rows stay in their registers for both).
-// Head dim 128: 8-11 form A_e; 12-15 form B_e and fold.
-// Every thread starts with 128 registers; the issuer warpgroup keeps 40 (setmaxnreg) and the others share the rest.
+// Warps (512 threads, four aligned warpgroups): 0 issuer of U (head dim 64: after loading the tiles; head dim 128:
+// of U and W); 1 TMEM owner and issuer of S; 2 issuer of dP; 3 issuer of W (head dim 128: TMA producer of the
+// ring); 4-7 and 8-11 two compute groups, each forming 32 of the 64 columns of every unit (P, G); 12-15 form A_e
+// and B_e of the next sweep, then fold U, W of the last one into dQ / dK2 / dV2 (head dim 64: the q and dO rows
+// stay in their registers for both).
+// Every thread starts with 128 registers; the issuer warpgroup keeps 40 (setmaxnreg), the compute groups 120
+// each and the fold group takes 232.
 // TMEM columns: S / dP buffer x -> S/P [128x, 128x+64), dP/G [128x+64, 128x+128); P and G (bf16, 16 columns per
-// 32 keys) overwrite the first half of the S and dP columns of the same keys,
-// so a buffer is busy from the issue of S / dP until the U / W products of its unit are done.  Head dim 64
-// has three such buffers in flight (issue, compute and U / W of different units overlap) and one U / W
-// accumulator pair [384, 512), which the fold group reads into registers before the next sweep's first
-// product; head dim 128 has two buffers (its ring has two slots) and U / W per sweep parity at [256 + 128p, +128).
+// 32 keys) overwrite the first half of the S and dP columns of the same keys - columns that the writing compute
+// group has itself read - so a buffer is busy from the issue of S / dP until the U / W products of its unit are
+// done.  Head dim 64 has three such buffers in flight (issue, compute and U / W of different units overlap) and
+// one U / W accumulator pair [384, 512), which the fold group reads into registers before the next sweep's
+// first product; head dim 128 has two buffers and U / W per sweep parity at [256 + 128p, +128).
 #pragma once
 #include "sa2_tc_bwd_k1.cuh"
 
@@ -54,9 +54,9 @@ constexpr int BQ_THREADS = 512;
 // thread; a group can only grow by what another has released, or its setmaxnreg never returns, so the
 // four budgets must add up to 4 * 128.
 constexpr int BQ_REGS_LAUNCH = 128, BQ_REGS_ISSUE = 40, BQ_REGS_COMPUTE = 120;
-// head dim 64: warps 8-11 are a compute group; the fold group holds dQ, the q and dO rows, and either the next
-// k2 / v2 rows or a k2 row and chunks of U and W (232);
-// head dim 128: the builders hold a whole q row and k2 row (144), the fold group dQ and a whole dO row and v2 row (208)
+// The fold group (232) holds dQ and, at head dim 64, the q and dO rows, plus either the operand rows of the next
+// sweep or a k2 row and chunks of U and W.  (With one compute group at head dim 128 - NCG = 1 - warps 8-11 form
+// A_e with 144 registers and the fold group keeps 208.)
 template <int D> struct BqCfg {
     static constexpr int CH = D / 64;                            // channel halves = CTAs per (query tile, split)
     static constexpr int KSTEPS = D / 16;                        // K = 16 steps of S and dP
