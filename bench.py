@@ -333,18 +333,44 @@ def load_traffic():
 
 def timed_operator(sa, _lib, tensors, w1, w2, kernel, steps, flush):
     """Per-step CUDA-event timing on the current stream, L2 flushed between steps: the forward and the
-    backward entry points as a user calls them."""
+    backward entry points.  Each is captured once into a CUDA graph (the same sa2_fwd / sa2_bwd calls on the
+    capturing stream) and replayed per step, so that a slow or busy host cannot leave the GPU idle between
+    the launches of a step; if the capture fails the calls are made directly.  Returns the two lists of
+    milliseconds and how the steps were launched."""
     q, k1, k2, v1, v2, do = tensors
+    how = "direct calls"
+    run_f = run_b = None
+    try:
+        gf, gb = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gf):
+            out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=kernel)
+        call = sa.BackwardCall(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=kernel)
+        with torch.cuda.graph(gb):
+            call.launch(0)
+        gf.replay()
+        gb.replay()
+        torch.cuda.synchronize()
+        run_f, run_b, how = gf.replay, gb.replay, "CUDA graphs of the forward call and of the backward call, replayed per step"
+    except Exception as e:      # noqa: BLE001 - any capture problem falls back to plain launches
+        sys.stderr.write("bench: graph capture failed (%s); launching directly\n" % (e,))
+        torch.cuda.synchronize()
+        state = {}
+
+        def run_f():
+            state["fwd"] = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=kernel)
+
+        def run_b():
+            sa.sa2_backward(q, k1, k2, v1, v2, state["fwd"][0], state["fwd"][1], do, w1, w2, kernel=kernel)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     for s in range(steps):
         flush.zero_()
         ev[s][0].record()
-        out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=kernel)
+        run_f()
         ev[s][1].record()
-        sa.sa2_backward(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=kernel)
+        run_b()
         ev[s][2].record()
     torch.cuda.synchronize()
-    return [e[0].elapsed_time(e[1]) for e in ev], [e[1].elapsed_time(e[2]) for e in ev]
+    return [e[0].elapsed_time(e[1]) for e in ev], [e[1].elapsed_time(e[2]) for e in ev], how
 
 
 def timed_kernels(sa, _lib, tensors, w1, w2, kernel, steps, flush):
@@ -537,7 +563,7 @@ def main():
     barrier(world)
     if rank == 0:
         sampler.start()
-    fwd_ms, bwd_ms = timed_operator(sa, _lib, devt, w1, w2, args.kernel, steps, flush)
+    fwd_ms, bwd_ms, launch_how = timed_operator(sa, _lib, devt, w1, w2, args.kernel, steps, flush)
     barrier(world)
     total_ms = reduce_max(sum(fwd_ms) + sum(bwd_ms), world)
     clocks = sampler.stop() if rank == 0 else None
@@ -628,7 +654,7 @@ def main():
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, **cfg, "global_batch": cfg["b"] * world, "kernel": args.kernel,
                    "sharding": "batch x head per rank, no collective",
-                   "l2": "256 MB buffer written between timed steps"},
+                   "l2": "256 MB buffer written between timed steps", "launch": launch_how},
         "tokens_per_s": cfg["b"] * cfg["n"] * world / (ms_per_step * 1e-3),
         "e2e": e2e,
         "gpu_launches": launches * steps,
