@@ -342,10 +342,12 @@ def timed_operator(sa, _lib, tensors, w1, w2, kernel, steps, flush):
     run_f = run_b = None
     try:
         gf, gb = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gf):
+        # thread-local capture: what other threads of the process do meanwhile (a collective library's watchdog)
+        # neither joins nor breaks the capture
+        with torch.cuda.graph(gf, capture_error_mode="thread_local"):
             out, lse = sa.sa2_forward(q, k1, k2, v1, v2, w1, w2, kernel=kernel)
         call = sa.BackwardCall(q, k1, k2, v1, v2, out, lse, do, w1, w2, kernel=kernel)
-        with torch.cuda.graph(gb):
+        with torch.cuda.graph(gb, capture_error_mode="thread_local"):
             call.launch(0)
         gf.replay()
         gb.replay()
