@@ -511,6 +511,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
     ap.add_argument("--no-extra", action="store_true", help="skip the sequence-sharded and long-sequence records")
+    ap.add_argument("--e2e-chunk", type=int, default=0, help="batch elements per chunk of the host-buffer leg (default: half the batch)")
     args = ap.parse_args()
     if args.workload == "C4":
         if args.impl == "reference":
@@ -576,7 +577,7 @@ def main():
     if not (args.no_e2e or big):
         from simplicial_attention_b200.host import HostPipeline
         outs_h = [torch.empty_like(t).pin_memory() for t in [host[0]] + host[:5]]
-        pipe = HostPipeline(dev, w1=w1, w2=w2, chunk=max(1, cfg["b"] // 2), kernel=args.kernel)
+        pipe = HostPipeline(dev, w1=w1, w2=w2, chunk=args.e2e_chunk or max(1, cfg["b"] // 2), kernel=args.kernel)
         for _ in range(2):
             pipe.run(host, outs_h)
         pipe.synchronize()
