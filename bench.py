@@ -511,7 +511,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
     ap.add_argument("--no-extra", action="store_true", help="skip the sequence-sharded and long-sequence records")
-    ap.add_argument("--e2e-chunk", type=int, default=0, help="batch elements per chunk of the host-buffer leg (default: half the batch)")
+    ap.add_argument("--e2e-chunk", type=int, default=0, help="batch elements per chunk of the host-buffer leg (default: the whole batch; copies then overlap the kernels of the neighbouring steps)")
     args = ap.parse_args()
     if args.workload == "C4":
         if args.impl == "reference":
@@ -577,8 +577,8 @@ def main():
     if not (args.no_e2e or big):
         from simplicial_attention_b200.host import HostPipeline
         outs_h = [torch.empty_like(t).pin_memory() for t in [host[0]] + host[:5]]
-        pipe = HostPipeline(dev, w1=w1, w2=w2, chunk=args.e2e_chunk or max(1, cfg["b"] // 2), kernel=args.kernel)
-        for _ in range(2):
+        pipe = HostPipeline(dev, w1=w1, w2=w2, chunk=args.e2e_chunk or cfg["b"], kernel=args.kernel)
+        for _ in range(max(2, int(os.environ.get("SA2_E2E_WARMUP", "2")))):
             pipe.run(host, outs_h)
         pipe.synchronize()
         pipe.record_copies()
@@ -586,7 +586,7 @@ def main():
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            pipe.run(host, outs_h)      # batch chunks on three streams: copy-in, compute and copy-out overlap, also across steps
+            pipe.run(host, outs_h)      # three streams: copy-in, compute and copy-out of consecutive steps (and chunks) overlap
         pipe.join()
         e1.record()
         barrier(world)
