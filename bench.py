@@ -10,15 +10,17 @@ runs that batch on its own GPU (batch x head sharding, no collective on the
 data path), so the global batch is 4*N and scaling is weak.
 
 Prints ONE JSON line:
-  value     whole-job TFLOP/s with the inputs resident in HBM, counting only
+  value     whole-job TFLOP/s with the inputs resident in HBM (the timed steps
+            replay CUDA graphs of the sa2_fwd and sa2_bwd calls), counting only
             algorithmic work: 14*d flop per unmasked (i, j, k) triple
             (4*d forward, 10*d backward); masked cells, the elementwise
             products, the softmax and any recomputation count zero;
   e2e       the same metric through the package's host-buffer call
             (HostPipeline.run) with pinned HOST tensors: host->device copy of
             q, k, k', v, v', dO and device->host copy of out and the five
-            gradients inside the timed region, overlapped with the kernels by
-            batch chunks (sequence sharding: the autograd API, serial copies);
+            gradients inside the timed region, on three streams so that they
+            overlap the kernels of the neighbouring steps (--e2e-chunk cuts a
+            call into batch chunks that overlap within the call);
   roofline  the dominant kernel (timed alone, live, with CUDA events) against the
             measured burst bf16 tensor peak of this pool's B200s, the sustained
             figure beside it; `kernels` lists all three tensor-core kernels;
@@ -578,7 +580,7 @@ def main():
         from simplicial_attention_b200.host import HostPipeline
         outs_h = [torch.empty_like(t).pin_memory() for t in [host[0]] + host[:5]]
         pipe = HostPipeline(dev, w1=w1, w2=w2, chunk=args.e2e_chunk or cfg["b"], kernel=args.kernel)
-        for _ in range(max(2, int(os.environ.get("SA2_E2E_WARMUP", "2")))):
+        for _ in range(3):
             pipe.run(host, outs_h)
         pipe.synchronize()
         pipe.record_copies()
