@@ -58,3 +58,21 @@ def test_distinct_value_head_dim_is_rejected_at_construction():
     with pytest.raises(ValueError):
         sa.SlidingWindowTwoSimplicialMHA(dim=64, heads=2, dim_head=32, dim_head_values=16)
     sa.SlidingWindowTwoSimplicialMHA(dim=64, heads=2, dim_head=32, dim_head_values=32)      # equal is fine
+
+
+def test_cpu_binding_is_a_no_op_without_a_gpu():
+    """bind_to_device_cpus only narrows the affinity mask when NVML names CPUs local to the GPU; without
+    a device it must leave the process alone and say so."""
+    import os
+    from simplicial_attention_b200.host import bind_to_device_cpus
+    before = os.sched_getaffinity(0)
+    if not torch.cuda.is_available():
+        assert bind_to_device_cpus("cuda:0") is None
+        assert os.sched_getaffinity(0) == before
+
+
+def test_wait_accounting_tool_names_every_kernel():
+    """The diagnostic front end knows the three tensor-core kernels and builds beside the normal library."""
+    from simplicial_attention_b200 import waitprof, build
+    assert sorted(waitprof.SLOTS) == ["dk1_dv1", "dq_dk2_dv2", "fwd"]
+    assert waitprof.PROF_LIB != build.LIB and waitprof.PROF_LIB.endswith("libsa2_prof.so")
