@@ -400,6 +400,14 @@ __device__ __forceinline__ int bq_compute(const BqParams &P, const BqGeom &g, in
 #pragma unroll 1
                 for (int ch = C::NCG == 2 ? cg : 0; ch < ch_end; ++ch) {
                     uint32_t sv[32], dv[32], pp[16], gg[16];
+                    // no row of this warp has a valid column among these 32: P = G = 0 without reading S / dP
+                    if (__all_sync(0xffffffffu, hi < ch * 32 || lo >= ch * 32 + 31)) {
+#pragma unroll
+                        for (int x = 0; x < 16; ++x) { pp[x] = 0u; gg[x] = 0u; }
+                        tmem_st16(lane_addr + buf * 128 + ch * 32, pp);
+                        tmem_st16(lane_addr + buf * 128 + 64 + ch * 32, gg);
+                        continue;
+                    }
 #ifdef SA2_PROF
                     const long long seg_t0 = clock64();
 #endif
