@@ -631,7 +631,7 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
         const int kk = i + kp.off2 - e;
         const bool ok = row_ok && kk >= 0;
         // the first half of the k2 row is fetched before the wait, so that its latency overlaps the end of the
-        // sweep; the second half with the second half of U and W
+        // sweep; the second half with U
         const __nv_bfloat16 *kr = k2 + elem_off(kp.k2, b, ok ? kk : 0, hk);
         uint4 k2r[4];
 #pragma unroll
@@ -646,7 +646,6 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
 #endif
         const int arow = r + kp.w2 - 1 - e;           // slab row of this thread in this sweep
         const bool fresh = BqAcc<D>::RING && (e == 0 || r == 0);      // ring: nothing has been added to the row yet
-        float *ak = acc_k + (size_t)arow * BQ_ACC_STRIDE, *av = acc_v + (size_t)arow * BQ_ACC_STRIDE;      // (padded layout)
         if (BqAcc<D>::RING && v >= 1 && warp == 12) {
             // the top row of the last sweep is complete: it goes to the slab before thread 0 reuses its place
             const int trow = TQ - 1 + kp.w2 - e, arr = lane >> 4, c4 = (lane & 15) * 4;
@@ -654,88 +653,103 @@ __device__ __forceinline__ int bq_fold_body(const BqParams &P, const BqGeom &g, 
             *reinterpret_cast<float4 *>(slab + ((size_t)arr * (127 + kp.w2) + trow) * D + c4) = t;
             __syncwarp();
         }
-        constexpr int CW = 32;                        // channels per step
+        const bool add = ok || BqAcc<D>::RING;       // (a ring row is written even when this thread has nothing to add)
+        // eight channels of one accumulator row += x
+        auto rmw8 = [&](float *acc, int col, const float (&x)[8]) {
+            if constexpr (BqAcc<D>::RING) {
+                // both 16-byte pieces are read before either is written: the swizzled addresses hide from the
+                // compiler that they are distinct, and it would order the second read after the first write
+                float4 *p0 = reinterpret_cast<float4 *>(acc + BqAcc<D>::off(arow, col));
+                float4 *p1 = reinterpret_cast<float4 *>(acc + BqAcc<D>::off(arow, col + 4));
+                float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0;
+                if (!fresh) { t0 = *p0; t1 = *p1; }
+                t0.x += x[0]; t0.y += x[1]; t0.z += x[2]; t0.w += x[3];
+                t1.x += x[4]; t1.y += x[5]; t1.z += x[6]; t1.w += x[7];
+                *p0 = t0;
+                *p1 = t1;
+            } else {
+                float4 *p = reinterpret_cast<float4 *>(acc + (size_t)arow * BQ_ACC_STRIDE + col);
+                float4 t0 = p[0], t1 = p[1];
+                t0.x += x[0]; t0.y += x[1]; t0.z += x[2]; t0.w += x[3];
+                t1.x += x[4]; t1.y += x[5]; t1.z += x[6]; t1.w += x[7];
+                p[0] = t0;
+                p[1] = t1;
+            }
+        };
+        // W first, then U, 32 channels at a time: only 32 registers of U / W are live at once, which keeps this
+        // group within its budget without spills (the accumulator pair is released after the last read).
+        {
+            uint4 dr[8];
 #pragma unroll
-        for (int ch = 0; ch < 64 / CW; ++ch) {
-            uint4 qr[CW / 8], dr[CW / 8];
+            for (int c8 = 0; c8 < 8; ++c8) {
+                if constexpr (D == 64) dr[c8] = dv[c8];
+                else dr[c8] = __ldg(reinterpret_cast<const uint4 *>(dorow + c8 * 8));
+            }
 #pragma unroll
-            for (int v8 = 0; v8 < CW / 8; ++v8) {
-                if constexpr (D == 64) {
-                    qr[v8] = qv[ch * (CW / 8) + v8];
-                    dr[v8] = dv[ch * (CW / 8) + v8];
-                } else {
-                    qr[v8] = __ldg(reinterpret_cast<const uint4 *>(qrow + ch * CW + v8 * 8));
-                    dr[v8] = __ldg(reinterpret_cast<const uint4 *>(dorow + ch * CW + v8 * 8));
+            for (int hf = 0; hf < 2; ++hf) {
+                uint32_t w[32];
+                tmem_ld32(lane_addr + C::UW0 + wb * 128 + 64 + hf * 32, w);
+                tmem_wait_ld();
+                if (add) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        const int c8 = hf * 4 + c4;
+                        const uint32_t dw[4] = {dr[c8].x, dr[c8].y, dr[c8].z, dr[c8].w};
+                        float xv[8];
+#pragma unroll
+                        for (int z = 0; z < 4; ++z) {
+                            const __nv_bfloat162 d2 = *reinterpret_cast<const __nv_bfloat162 *>(&dw[z]);
+                            const int x = c4 * 8 + z * 2;
+                            xv[z * 2] = ok ? __uint_as_float(w[x]) * __low2float(d2) : 0.f;
+                            xv[z * 2 + 1] = ok ? __uint_as_float(w[x + 1]) * __high2float(d2) : 0.f;
+                        }
+                        rmw8(acc_v, c8 * 8, xv);
+                    }
                 }
             }
-            uint32_t u[CW], w[CW];
-            tmem_ld32(lane_addr + C::UW0 + wb * 128 + ch * CW, u);
-            tmem_ld32(lane_addr + C::UW0 + wb * 128 + 64 + ch * CW, w);
-            if (ch == 1) {
+        }
+        {
+            uint4 qr[8];
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc)
-                    k2r[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kr + 32 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            for (int c8 = 0; c8 < 8; ++c8) {
+                if constexpr (D == 64) qr[c8] = qv[c8];
+                else qr[c8] = __ldg(reinterpret_cast<const uint4 *>(qrow + c8 * 8));
             }
-            tmem_wait_ld();
-            if (ch == 64 / CW - 1) {
-                // U and W of the sweep are in registers: the tensor cores may overwrite them
-                tc_fence_before();
-                mbar_arrive(&bars[BQ_W_EMPTY + wb]);
-            }
-            if (ok || BqAcc<D>::RING) {              // (a ring row is written even when this thread has nothing to add)
 #pragma unroll
-                for (int v8 = 0; v8 < CW / 8; ++v8) {
-                    const uint4 kraw = k2r[v8];
-                    const uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
-                    const uint32_t qw[4] = {qr[v8].x, qr[v8].y, qr[v8].z, qr[v8].w};
-                    const uint32_t dw[4] = {dr[v8].x, dr[v8].y, dr[v8].z, dr[v8].w};
-                    float xk[8], xv[8];
+            for (int hf = 0; hf < 2; ++hf) {
+                uint32_t u[32];
+                tmem_ld32(lane_addr + C::UW0 + wb * 128 + hf * 32, u);
+                if (hf == 1) {
 #pragma unroll
-                    for (int z = 0; z < 4; ++z) {
-                        const __nv_bfloat162 k2v = *reinterpret_cast<const __nv_bfloat162 *>(&kw[z]);
-                        const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162 *>(&qw[z]);
-                        const __nv_bfloat162 d2 = *reinterpret_cast<const __nv_bfloat162 *>(&dw[z]);
-                        const int x = v8 * 8 + z * 2;
-                        const float u0 = __uint_as_float(u[x]), u1 = __uint_as_float(u[x + 1]);
-                        dq[ch * CW + x] = fmaf(u0, __low2float(k2v), dq[ch * CW + x]);
-                        dq[ch * CW + x + 1] = fmaf(u1, __high2float(k2v), dq[ch * CW + x + 1]);
-                        const bool add = ok || !BqAcc<D>::RING;      // (the padded layout skips rows with nothing to add)
-                        xk[z * 2] = add ? u0 * __low2float(q2) : 0.f;
-                        xk[z * 2 + 1] = add ? u1 * __high2float(q2) : 0.f;
-                        xv[z * 2] = add ? __uint_as_float(w[x]) * __low2float(d2) : 0.f;
-                        xv[z * 2 + 1] = add ? __uint_as_float(w[x + 1]) * __high2float(d2) : 0.f;
-                    }
-                    if constexpr (BqAcc<D>::RING) {
-                        // both 16-byte pieces of both rows are read before any is written: the swizzled addresses
-                        // hide from the compiler that they are distinct, and it would order every read after the
-                        // last write
-                        float4 *pk[2], *pv[2], tk[2], tv[2];
+                    for (int cc = 0; cc < 4; ++cc)
+                        k2r[cc] = ok ? __ldg(reinterpret_cast<const uint4 *>(kr + 32 + cc * 8)) : make_uint4(0u, 0u, 0u, 0u);
+                }
+                tmem_wait_ld();
+                if (hf == 1) {
+                    // U and W of the sweep are in registers (or already used): the tensor cores may overwrite them
+                    tc_fence_before();
+                    mbar_arrive(&bars[BQ_W_EMPTY + wb]);
+                }
+                if (add) {
 #pragma unroll
-                        for (int f4 = 0; f4 < 2; ++f4) {
-                            const int off = BqAcc<D>::off(arow, ch * CW + v8 * 8 + f4 * 4);
-                            pk[f4] = reinterpret_cast<float4 *>(acc_k + off);
-                            pv[f4] = reinterpret_cast<float4 *>(acc_v + off);
-                            tk[f4] = tv[f4] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (!fresh) { tk[f4] = *pk[f4]; tv[f4] = *pv[f4]; }
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        const int c8 = hf * 4 + c4;
+                        const uint4 kraw = k2r[c4];
+                        const uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
+                        const uint32_t qw[4] = {qr[c8].x, qr[c8].y, qr[c8].z, qr[c8].w};
+                        float xk[8];
+#pragma unroll
+                        for (int z = 0; z < 4; ++z) {
+                            const __nv_bfloat162 k2v = *reinterpret_cast<const __nv_bfloat162 *>(&kw[z]);
+                            const __nv_bfloat162 q2 = *reinterpret_cast<const __nv_bfloat162 *>(&qw[z]);
+                            const int x = c4 * 8 + z * 2;
+                            const float a0 = __uint_as_float(u[x]), a1 = __uint_as_float(u[x + 1]);
+                            dq[c8 * 8 + z * 2] = fmaf(a0, __low2float(k2v), dq[c8 * 8 + z * 2]);
+                            dq[c8 * 8 + z * 2 + 1] = fmaf(a1, __high2float(k2v), dq[c8 * 8 + z * 2 + 1]);
+                            xk[z * 2] = ok ? a0 * __low2float(q2) : 0.f;
+                            xk[z * 2 + 1] = ok ? a1 * __high2float(q2) : 0.f;
                         }
-#pragma unroll
-                        for (int f4 = 0; f4 < 2; ++f4) {
-                            tk[f4].x += xk[f4 * 4]; tk[f4].y += xk[f4 * 4 + 1]; tk[f4].z += xk[f4 * 4 + 2]; tk[f4].w += xk[f4 * 4 + 3];
-                            tv[f4].x += xv[f4 * 4]; tv[f4].y += xv[f4 * 4 + 1]; tv[f4].z += xv[f4 * 4 + 2]; tv[f4].w += xv[f4 * 4 + 3];
-                            *pk[f4] = tk[f4];
-                            *pv[f4] = tv[f4];
-                        }
-                    } else {
-#pragma unroll
-                        for (int f4 = 0; f4 < 2; ++f4) {
-                            float4 *pk = reinterpret_cast<float4 *>(ak + ch * CW + v8 * 8 + f4 * 4);
-                            float4 *pv = reinterpret_cast<float4 *>(av + ch * CW + v8 * 8 + f4 * 4);
-                            float4 tk = *pk, tv = *pv;
-                            tk.x += xk[f4 * 4]; tk.y += xk[f4 * 4 + 1]; tk.z += xk[f4 * 4 + 2]; tk.w += xk[f4 * 4 + 3];
-                            tv.x += xv[f4 * 4]; tv.y += xv[f4 * 4 + 1]; tv.z += xv[f4 * 4 + 2]; tv.w += xv[f4 * 4 + 3];
-                            *pk = tk;
-                            *pv = tv;
-                        }
+                        rmw8(acc_k, c8 * 8, xk);
                     }
                 }
             }
